@@ -1,0 +1,117 @@
+/*
+ * b200_sgemm — C ABI of the B200 (sm_100a) FP32 GEMM library.
+ *
+ * This is the boundary a binding of the reference's operator would call: plain pointers, sizes and
+ * integers only.  Matrices are FP32 in device memory; layouts are 0 = row-major, 1 = col-major
+ * (the enumerator order of rocm_sgemm::m_layout, rocm_sgemm/include/rocm_sgemm/kernel/common.hpp:36-40).
+ * Every function returns a status (0 = OK) instead of throwing or exiting; the C++ shim
+ * include/rocm_sgemm/gemm.hpp turns a non-zero status into std::runtime_error, the one throwing
+ * behaviour the reference has (rocm_sgemm/include/rocm_sgemm/kernel_launcher.hpp:89-94).
+ * There is no CPU fallback: without a CUDA device the compute entry points return a CUDA error.
+ */
+#ifndef B200_SGEMM_H
+#define B200_SGEMM_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_SGEMM_ROW_MAJOR 0
+#define B200_SGEMM_COL_MAJOR 1
+
+/* status codes; positive values are cudaError_t codes reported by the CUDA runtime */
+#define B200_SGEMM_OK 0
+#define B200_SGEMM_INVALID_ARGUMENT (-1) /* null pointer, zero dimension, bad layout, bad leading dimension */
+#define B200_SGEMM_NO_KERNEL (-2)        /* no kernel built for (variant, layout, alignment) */
+#define B200_SGEMM_WORKSPACE_TOO_SMALL (-3)
+#define B200_SGEMM_UNSUPPORTED_SIZE (-4) /* a dimension exceeds what the kernels index (2^31-1) */
+
+/* Tile parameters of one kernel variant: the reference's nine (struct gemm_params emitted by
+ * rocm_sgemm/config/generate_config.py:100-111) followed by the CUDA-side additions. */
+typedef struct b200_sgemm_params
+{
+    int block_size;        /* threads per CTA */
+    int block_m;           /* CTA tile rows */
+    int block_n;           /* CTA tile columns */
+    int block_k;           /* K depth of one staged tile */
+    int warp_tile_m_count; /* thread sub-tiles per thread along m */
+    int warp_tile_n_count; /* thread sub-tiles per thread along n */
+    int thread_tile_m;     /* rows of one thread sub-tile (one shared-memory vector read) */
+    int thread_tile_n;     /* columns of one thread sub-tile */
+    int threads_n;         /* lanes of a warp along n */
+    int stages;            /* depth of the shared-memory ring */
+    int fma_mode;          /* 0 scalar fma.rn.f32, 1 fma.rn.f32x2 (A duplicated), 2 fma.rn.f32x2 (2x2 diagonal) */
+    int raster;            /* 0 row-major tile order, 1 grouped bands, 2 Hilbert curve */
+    int min_blocks;        /* CTAs per SM the register budget is sized for */
+    int split_k;           /* K slices chosen for the looked-up problem (1 = none) */
+} b200_sgemm_params;
+
+/* C = A*B, C overwritten, packed matrices, asynchronous on `cuda_stream` (a cudaStream_t; NULL = the
+ * default stream), no synchronisation and no error check of the kernel's execution.
+ * Replaces rocm_sgemm::gemm<layout_C, layout_A, layout_B>(C, A, B, M, N, K, stream)
+ * (rocm_sgemm/include/rocm_sgemm/gemm.hpp:51-52, rocm_sgemm/src/gemm.cpp:8-41): same argument order
+ * (C, A, B), same semantics (alpha = 1, beta = 0, inputs untouched), additionally correct for ragged
+ * M, N, K.  A is MxK, B is KxN, C is MxN.  When the tuned table asks for split-K the library takes
+ * the partial-sum buffer from an internal per-(device, stream) arena that grows on demand. */
+int b200_sgemm(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M, size_t N,
+               size_t K, void* cuda_stream);
+
+/* Same operation with everything the drop-in entry decides made explicit: leading dimensions in
+ * elements (0 = packed), a forced kernel variant (-1 = look up the table, as
+ * detail::find_best_config does in rocm_sgemm/src/gemm.cpp:12), a forced split-K (0 = the table's)
+ * and a caller-owned workspace for the split-K partial sums (may be NULL when the effective split
+ * is 1; otherwise at least b200_sgemm_workspace_bytes()).  The tuner drives kernels through this
+ * entry the way the reference's tuner launches a JIT-compiled instantiation directly
+ * (rocm_sgemm/config/tuner.cpp:419-429); the column-sharded multi-GPU driver uses the leading
+ * dimensions. */
+int b200_sgemm_ex(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
+                  size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant, int split_k, void* workspace,
+                  size_t workspace_bytes, void* cuda_stream);
+
+/* Bytes of split-K workspace b200_sgemm_ex needs for this call (0 when the effective split is 1). */
+size_t b200_sgemm_workspace_bytes(int layout_c, int layout_a, int layout_b, size_t M, size_t N, size_t K, int variant,
+                                  int split_k);
+
+/* Table lookup without launching: fills `out` (may be NULL) and `variant` (may be NULL).
+ * Replaces rocm_sgemm::get_gemm_params(m, n, k, layout_c, layout_a, layout_b)
+ * (rocm_sgemm/config/generate_config.py:282-303) and detail::find_best_config (:241-267). */
+int b200_sgemm_select_config(int layout_c, int layout_a, int layout_b, size_t M, size_t N, size_t K,
+                             b200_sgemm_params* out, int* variant);
+
+/* Number of kernel variants (the reference's KERNEL_VARIANTS, generate_config.py:97) and their
+ * parameters (detail::kernel_configs, :113-124). */
+int b200_sgemm_num_variants(void);
+int b200_sgemm_get_variant(int variant, b200_sgemm_params* out);
+
+/* The tuned table itself (detail::sorted_config_map, generate_config.py:156-171):
+ * mnk = {M, N, K}; layouts = {A, B, C}. */
+int b200_sgemm_num_entries(void);
+int b200_sgemm_get_entry(int index, size_t mnk[3], int layouts[3], int* variant, int* split_k);
+
+/* 1 when a kernel exists for (variant, layout index A*4+B*2+C, aligned 0/1), as a non-null
+ * kernel_table slot does in the reference (rocm_sgemm/include/rocm_sgemm/kernel_lookup.hpp:39). */
+int b200_sgemm_has_kernel(int variant, int layout_index, int aligned);
+
+/* The selection rule applied to a caller-supplied table (host only, no CUDA): `keys` holds `count`
+ * rows of {m, n, k, layout_a, layout_b, layout_c} sorted the way the reference sorts them.
+ * Returns the chosen row or -1 for an empty table. */
+int b200_sgemm_select_in_table(const size_t* keys, size_t count, size_t M, size_t N, size_t K, int layout_a,
+                               int layout_b, int layout_c);
+
+/* Register-only FP32 FMA throughput probe on the current device: the measured FMA-pipe ceiling the
+ * GEMM numbers are quoted against.  mode 0 = fma.rn.f32, 1 = fma.rn.f32x2.  Writes the elapsed
+ * milliseconds of one launch (CUDA events on `cuda_stream`) and the FLOPs it performed. */
+int b200_sgemm_fma_peak(int mode, int iterations, float* elapsed_ms, double* flops, void* cuda_stream);
+
+/* Frees the internal split-K arenas of every device (optional; they are also freed at unload). */
+int b200_sgemm_shutdown(void);
+
+/* Human-readable text for a status returned by any function above. */
+const char* b200_sgemm_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_SGEMM_H */

@@ -1,0 +1,220 @@
+"""rocm_sgemm_b200 — Python front end of the B200 FP32 GEMM library.
+
+A thin ctypes binding of the C ABI in include/b200_sgemm.h that mirrors the reference's operator
+surface: `gemm(layout_C, layout_A, layout_B, C, A, B, M, N, K, stream)` for
+rocm_sgemm::gemm<layout_C, layout_A, layout_B>(C, A, B, M, N, K, stream)
+(rocm_sgemm/include/rocm_sgemm/gemm.hpp:51-52) and `get_gemm_params` for
+rocm_sgemm::get_gemm_params (rocm_sgemm/config/generate_config.py:282-303).
+
+Device memory is the caller's: arguments are raw device addresses (ints) or objects with a
+`data_ptr()` method (torch tensors are used for device memory and streams only).  There is no CPU
+path: if the compiled library is missing, importing the compute entry points raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import os
+from dataclasses import dataclass
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200_sgemm.so")
+CUBLAS_LIB_PATH = os.path.join(_HERE, "libb200_cublas_wrapper.so")
+
+
+class m_layout(enum.IntEnum):
+    """rocm_sgemm::m_layout (rocm_sgemm/include/rocm_sgemm/kernel/common.hpp:36-40)."""
+    row_major = 0
+    col_major = 1
+
+
+ROW, COL = m_layout.row_major, m_layout.col_major
+
+OK = 0
+INVALID_ARGUMENT = -1
+NO_KERNEL = -2
+WORKSPACE_TOO_SMALL = -3
+UNSUPPORTED_SIZE = -4
+
+
+class _Params(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "block_size", "block_m", "block_n", "block_k", "warp_tile_m_count", "warp_tile_n_count", "thread_tile_m",
+        "thread_tile_n", "threads_n", "stages", "fma_mode", "raster", "min_blocks", "split_k")]
+
+
+@dataclass(frozen=True)
+class gemm_params:
+    """struct gemm_params of the reference's generated header plus the CUDA-side knobs."""
+    block_size: int
+    block_m: int
+    block_n: int
+    block_k: int
+    warp_tile_m_count: int
+    warp_tile_n_count: int
+    thread_tile_m: int
+    thread_tile_n: int
+    threads_n: int
+    stages: int
+    fma_mode: int
+    raster: int
+    min_blocks: int
+    split_k: int
+
+    def nine(self) -> tuple:
+        return (self.block_size, self.block_m, self.block_n, self.block_k, self.warp_tile_m_count,
+                self.warp_tile_n_count, self.thread_tile_m, self.thread_tile_n, self.threads_n)
+
+
+class SgemmError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        super().__init__(f"b200_sgemm: {what} (status {status})")
+        self.status = status
+
+
+_lib = None
+_sz = ctypes.c_size_t
+_vp = ctypes.c_void_p
+
+EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sgemm_select_config",
+           "b200_sgemm_num_variants", "b200_sgemm_get_variant", "b200_sgemm_num_entries", "b200_sgemm_get_entry",
+           "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_shutdown",
+           "b200_sgemm_status_string")
+
+
+def lib() -> ctypes.CDLL:
+    """Load libb200_sgemm.so; raises if it has not been built (there is no fallback)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m rocm_sgemm_b200.build` "
+                          "(the library has no CPU or PyTorch fallback)")
+    l = ctypes.CDLL(LIB_PATH)
+    i = ctypes.c_int
+    l.b200_sgemm.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _vp]
+    l.b200_sgemm_ex.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, i, i, _vp, _sz, _vp]
+    l.b200_sgemm_workspace_bytes.argtypes = [i, i, i, _sz, _sz, _sz, i, i]
+    l.b200_sgemm_workspace_bytes.restype = _sz
+    l.b200_sgemm_select_config.argtypes = [i, i, i, _sz, _sz, _sz, ctypes.POINTER(_Params), ctypes.POINTER(i)]
+    l.b200_sgemm_get_variant.argtypes = [i, ctypes.POINTER(_Params)]
+    l.b200_sgemm_get_entry.argtypes = [i, ctypes.POINTER(_sz), ctypes.POINTER(i), ctypes.POINTER(i),
+                                       ctypes.POINTER(i)]
+    l.b200_sgemm_has_kernel.argtypes = [i, i, i]
+    l.b200_sgemm_select_in_table.argtypes = [ctypes.POINTER(_sz), _sz, _sz, _sz, _sz, i, i, i]
+    l.b200_sgemm_fma_peak.argtypes = [i, i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double), _vp]
+    l.b200_sgemm_status_string.argtypes = [i]
+    l.b200_sgemm_status_string.restype = ctypes.c_char_p
+    _lib = l
+    return l
+
+
+def status_string(status: int) -> str:
+    return lib().b200_sgemm_status_string(status).decode()
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise SgemmError(status, status_string(status))
+
+
+def _ptr(x) -> int:
+    if x is None:
+        return 0
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    return int(x)
+
+
+def _stream(stream) -> int:
+    """Accepts None (the current torch stream when torch is loaded, else the default stream), a raw
+    cudaStream_t value, or an object with a `cuda_stream` attribute (torch.cuda.Stream)."""
+    if stream is None:
+        try:
+            import torch
+            if torch.cuda.is_available():
+                return int(torch.cuda.current_stream().cuda_stream)
+        except ImportError:
+            pass
+        return 0
+    if hasattr(stream, "cuda_stream"):
+        return int(stream.cuda_stream)
+    return int(stream)
+
+
+def _to_params(p: _Params) -> gemm_params:
+    return gemm_params(*(getattr(p, n) for n, _ in _Params._fields_))
+
+
+def gemm(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, stream=None) -> None:
+    """C = A @ B on the device, C overwritten; asynchronous on `stream`.  Argument order follows the
+    reference: template arguments (layout_C, layout_A, layout_B), then (C, A, B, M, N, K, stream)."""
+    _check(lib().b200_sgemm(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K,
+                            _stream(stream)))
+
+
+def gemm_ex(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, lda: int = 0, ldb: int = 0, ldc: int = 0,
+            variant: int = -1, split_k: int = 0, workspace=None, workspace_bytes: int = 0, stream=None) -> None:
+    """The explicit form: leading dimensions (0 = packed), forced variant / split-K, caller workspace."""
+    _check(lib().b200_sgemm_ex(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K, lda,
+                               ldb, ldc, variant, split_k, _ptr(workspace), workspace_bytes, _stream(stream)))
+
+
+def workspace_bytes(layout_c, layout_a, layout_b, M, N, K, variant: int = -1, split_k: int = 0) -> int:
+    return int(lib().b200_sgemm_workspace_bytes(int(layout_c), int(layout_a), int(layout_b), M, N, K, variant,
+                                                split_k))
+
+
+def get_gemm_params(m: int, n: int, k: int, layout_c, layout_a, layout_b) -> gemm_params:
+    """rocm_sgemm::get_gemm_params(m, n, k, layout_c, layout_a, layout_b)."""
+    return select_config(m, n, k, layout_c, layout_a, layout_b)[0]
+
+
+def select_config(m, n, k, layout_c, layout_a, layout_b):
+    p, v = _Params(), ctypes.c_int(-1)
+    _check(lib().b200_sgemm_select_config(int(layout_c), int(layout_a), int(layout_b), m, n, k, ctypes.byref(p),
+                                          ctypes.byref(v)))
+    return _to_params(p), v.value
+
+
+def num_variants() -> int:
+    return int(lib().b200_sgemm_num_variants())
+
+
+def get_variant(idx: int) -> gemm_params:
+    p = _Params()
+    _check(lib().b200_sgemm_get_variant(idx, ctypes.byref(p)))
+    return _to_params(p)
+
+
+def table_entries() -> list:
+    """[(M, N, K, layout_A, layout_B, layout_C, variant, split_k), ...] in lookup order."""
+    l, out = lib(), []
+    for i in range(l.b200_sgemm_num_entries()):
+        mnk, lay, v, s = (_sz * 3)(), (ctypes.c_int * 3)(), ctypes.c_int(), ctypes.c_int()
+        _check(l.b200_sgemm_get_entry(i, mnk, lay, ctypes.byref(v), ctypes.byref(s)))
+        out.append((int(mnk[0]), int(mnk[1]), int(mnk[2]), lay[0], lay[1], lay[2], v.value, s.value))
+    return out
+
+
+def has_kernel(variant: int, layout_a, layout_b, layout_c, aligned: bool) -> bool:
+    return bool(lib().b200_sgemm_has_kernel(variant, int(layout_a) * 4 + int(layout_b) * 2 + int(layout_c),
+                                            1 if aligned else 0))
+
+
+def select_in_table(keys, m, n, k, layout_a, layout_b, layout_c) -> int:
+    """The selection rule over a caller-supplied sorted table of (m, n, k, la, lb, lc) rows."""
+    flat = (_sz * (6 * len(keys)))(*[int(x) for row in keys for x in row])
+    return int(lib().b200_sgemm_select_in_table(flat, len(keys), m, n, k, int(layout_a), int(layout_b),
+                                                int(layout_c)))
+
+
+def fma_peak(mode: int = 1, iterations: int = 4096, stream=None) -> dict:
+    """Register-only FMA probe: {'ms', 'flops', 'tflops'} for fma.rn.f32 (mode 0) or fma.rn.f32x2 (mode 1)."""
+    ms, fl = ctypes.c_float(), ctypes.c_double()
+    _check(lib().b200_sgemm_fma_peak(mode, iterations, ctypes.byref(ms), ctypes.byref(fl), _stream(stream)))
+    return {"ms": ms.value, "flops": fl.value, "tflops": fl.value / (ms.value * 1e-3) / 1e12}
+
+
+def shutdown() -> None:
+    _check(lib().b200_sgemm_shutdown())
