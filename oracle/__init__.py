@@ -131,11 +131,12 @@ def sgemm_f64(lc, la, lb, A, B, M, N, K, rows=None, threads=1) -> np.ndarray:
 
 
 def error_metrics(lc, C, ref64, M, N, rows=None) -> dict:
-    """max_abs, max_rel (= |c-ref| / max(|ref|, rms(ref))) and rms(ref) over the row band."""
-    out = np.zeros(3, dtype=np.float64)
+    """max_abs, max_rel (= |c-ref| / max(|ref|, rms(ref))), rms(ref) and rms(c-ref) over the row band."""
+    out = np.zeros(4, dtype=np.float64)
     r0, r1 = _band(M, rows)
     lib().oracle_error_metrics(lc, _f(C), _d(ref64), M, N, r0, r1, _d(out))
-    return {"max_abs": float(out[0]), "max_rel": float(out[1]), "rms_ref": float(out[2])}
+    return {"max_abs": float(out[0]), "max_rel": float(out[1]), "rms_ref": float(out[2]),
+            "rms_err": float(out[3])}
 
 
 # --------------------------------------------------------------------------------------------

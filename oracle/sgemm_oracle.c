@@ -228,6 +228,7 @@ void oracle_sgemm_f64(int lc, int la, int lb, double* C, const float* A, const f
  *   out[0] = max |c - ref|
  *   out[1] = max |c - ref| / max(|ref|, rms(ref))      (the relative error the tolerance is stated on)
  *   out[2] = rms(ref) over the band
+ *   out[3] = rms(c - ref) over the band
  * Both matrices are indexed with layout lc. */
 void oracle_error_metrics(int lc, const float* C, const double* ref, size_t M, size_t N, size_t row_begin,
                           size_t row_end, double* out)
@@ -242,12 +243,13 @@ void oracle_error_metrics(int lc, const float* C, const double* ref, size_t M, s
             ++n;
         }
     double rms     = n ? sqrt(ss / (double)n) : 0.0;
-    double max_abs = 0.0, max_rel = 0.0;
+    double max_abs = 0.0, max_rel = 0.0, se = 0.0;
     for(size_t i = row_begin; i < row_end; ++i)
         for(size_t j = 0; j < N; ++j)
         {
             size_t p = idx(lc, M, N, i, j);
             double d = fabs((double)C[p] - ref[p]);
+            se += d * d;
             double s = fabs(ref[p]) > rms ? fabs(ref[p]) : rms;
             if(d > max_abs)
                 max_abs = d;
@@ -257,6 +259,7 @@ void oracle_error_metrics(int lc, const float* C, const double* ref, size_t M, s
     out[0] = max_abs;
     out[1] = max_rel;
     out[2] = rms;
+    out[3] = n ? sqrt(se / (double)n) : 0.0;
 }
 
 int oracle_max_threads(void)

@@ -18,7 +18,8 @@ import os
 from dataclasses import dataclass
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200_sgemm.so")
+# B200_SGEMM_LIB selects another build of the same ABI (the tuner loads candidate builds this way)
+LIB_PATH = os.environ.get("B200_SGEMM_LIB") or os.path.join(_HERE, "libb200_sgemm.so")
 CUBLAS_LIB_PATH = os.path.join(_HERE, "libb200_cublas_wrapper.so")
 
 
