@@ -45,6 +45,7 @@ typedef struct b200_sgemm_params
     int fma_mode;          /* 0 scalar fma.rn.f32, 1 fma.rn.f32x2 (A duplicated), 2 fma.rn.f32x2 (2x2 diagonal) */
     int raster;            /* 0 row-major tile order, 1 grouped bands, 2 Hilbert curve */
     int min_blocks;        /* CTAs per SM the register budget is sized for */
+    int pipeline;          /* 0 every warp stages and computes, 1 warp-specialised (TMA / producer warps + mbarriers) */
     int split_k;           /* K slices chosen for the looked-up problem (1 = none) */
 } b200_sgemm_params;
 
@@ -104,6 +105,12 @@ int b200_sgemm_select_in_table(const size_t* keys, size_t count, size_t M, size_
  * GEMM numbers are quoted against.  mode 0 = fma.rn.f32, 1 = fma.rn.f32x2.  Writes the elapsed
  * milliseconds of one launch (CUDA events on `cuda_stream`) and the FLOPs it performed. */
 int b200_sgemm_fma_peak(int mode, int iterations, float* elapsed_ms, double* flops, void* cuda_stream);
+
+/* Reads (and clears) the current device's kernel status word after synchronising the device:
+ * 0 = no kernel reported a problem; 1 / 2 = a warp-specialised kernel gave up a bounded wait on a
+ * shared-memory barrier (consumer / producer side) and its output is invalid.  Diagnostic only: the
+ * reference has no counterpart because its kernel has no waits that could time out. */
+int b200_sgemm_device_status(int* status);
 
 /* Frees the internal split-K arenas of every device (optional; they are also freed at unload). */
 int b200_sgemm_shutdown(void);

@@ -41,7 +41,7 @@ UNSUPPORTED_SIZE = -4
 class _Params(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "block_size", "block_m", "block_n", "block_k", "warp_tile_m_count", "warp_tile_n_count", "thread_tile_m",
-        "thread_tile_n", "threads_n", "stages", "fma_mode", "raster", "min_blocks", "split_k")]
+        "thread_tile_n", "threads_n", "stages", "fma_mode", "raster", "min_blocks", "pipeline", "split_k")]
 
 
 @dataclass(frozen=True)
@@ -60,6 +60,7 @@ class gemm_params:
     fma_mode: int
     raster: int
     min_blocks: int
+    pipeline: int
     split_k: int
 
     def nine(self) -> tuple:
@@ -79,7 +80,8 @@ _vp = ctypes.c_void_p
 
 EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sgemm_select_config",
            "b200_sgemm_num_variants", "b200_sgemm_get_variant", "b200_sgemm_num_entries", "b200_sgemm_get_entry",
-           "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_shutdown",
+           "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
+           "b200_sgemm_shutdown",
            "b200_sgemm_status_string")
 
 
@@ -104,6 +106,7 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_has_kernel.argtypes = [i, i, i]
     l.b200_sgemm_select_in_table.argtypes = [ctypes.POINTER(_sz), _sz, _sz, _sz, _sz, i, i, i]
     l.b200_sgemm_fma_peak.argtypes = [i, i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double), _vp]
+    l.b200_sgemm_device_status.argtypes = [ctypes.POINTER(i)]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
     _lib = l
@@ -215,6 +218,13 @@ def fma_peak(mode: int = 1, iterations: int = 4096, stream=None) -> dict:
     ms, fl = ctypes.c_float(), ctypes.c_double()
     _check(lib().b200_sgemm_fma_peak(mode, iterations, ctypes.byref(ms), ctypes.byref(fl), _stream(stream)))
     return {"ms": ms.value, "flops": fl.value, "tflops": fl.value / (ms.value * 1e-3) / 1e12}
+
+
+def device_status() -> int:
+    """Synchronises the current device and returns (then clears) its kernel status word; 0 = healthy."""
+    st = ctypes.c_int(0)
+    _check(lib().b200_sgemm_device_status(ctypes.byref(st)))
+    return st.value
 
 
 def shutdown() -> None:

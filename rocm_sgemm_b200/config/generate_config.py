@@ -27,11 +27,11 @@ from pathlib import Path
 
 NINE = ("block_size", "block_m", "block_n", "block_k", "warp_tile_m_count", "warp_tile_n_count",
         "thread_tile_m", "thread_tile_n", "threads_n")
-EXTRA_DEFAULTS = {"stages": 2, "fma_mode": 2, "raster": 1, "min_blocks": 1}
+EXTRA_DEFAULTS = {"stages": 2, "fma_mode": 2, "raster": 1, "min_blocks": 1, "pipeline": 0}
 VARIANT_FIELDS = NINE + tuple(EXTRA_DEFAULTS)
 
 # nominal default: 128x128x16 CTA tile, 256 threads, 8x8 per thread as 2x2 sub-tiles of 4x4
-DEFAULT_VARIANT = (256, 128, 128, 16, 2, 2, 4, 4, 8, 2, 2, 1, 1)
+DEFAULT_VARIANT = (256, 128, 128, 16, 2, 2, 4, 4, 8, 2, 2, 1, 1, 0)
 
 LAYOUT_VAL = {"row_major": 0, "col_major": 1}
 LAYOUTS = [(a, b, c) for a in (0, 1) for b in (0, 1) for c in (0, 1)]  # index = a*4 + b*2 + c
@@ -49,7 +49,7 @@ def variant_of(cfg: dict) -> tuple:
 def check_variant(v: tuple) -> str | None:
     """Constraint check shared with the tuner (the reference's is rocm_sgemm/config/tune.py:100-144).
     Returns None when the variant is buildable, else the reason."""
-    (bs, bm, bn, bk, wmc, wnc, tm, tn, threads_n, stages, fma_mode, raster, min_blocks) = v
+    (bs, bm, bn, bk, wmc, wnc, tm, tn, threads_n, stages, fma_mode, raster, min_blocks, pipeline) = v
     if any(x <= 0 for x in v[:10]) or min_blocks <= 0:
         return "non-positive parameter"
     if 32 % threads_n != 0:
@@ -74,8 +74,21 @@ def check_variant(v: tuple) -> str | None:
         return "packed FMA needs even thread_tile_n"
     if fma_mode == 2 and tm % 2:
         return "diagonal packing needs even thread_tile_m"
-    if stages * (bm + bn) * bk * 4 > SMEM_LIMIT:
+    if pipeline not in (0, 1):
+        return "unknown pipeline"
+    if stages * (bm + bn) * bk * 4 + (2 * stages * 8 + 16 if pipeline else 0) > SMEM_LIMIT:
         return "shared memory over 227 KB"
+    if pipeline == 1:
+        # warp-specialised kernel: 128-bit fragment reads only, TMA boxes of at most 256 elements,
+        # consumer warps + one producer warpgroup in one CTA
+        if tm not in (4, 8) or tn not in (4, 8):
+            return "warp-specialised kernel needs thread tiles of 4 or 8"
+        if bm > 256 or bn > 256 or bk > 256:
+            return "TMA box dimension over 256"
+        if bs + 128 > 1024:
+            return "consumer + producer threads over 1024"
+        if min_blocks != 1:
+            return "warp-specialised kernel is persistent: one CTA per SM"
     # per-thread accumulators must fit the register file
     if wmc * tm * wnc * tn > 192:
         return "accumulator tile over 192 registers"
@@ -115,7 +128,15 @@ def needed_pairs(variants, entries):
 
 
 def cfg_type(v: tuple) -> str:
-    return "TileConfig<" + ", ".join(str(x) for x in v) + ">"
+    return "TileConfig<" + ", ".join(str(x) for x in v[:13]) + ">"
+
+
+def kernel_header(v: tuple) -> str:
+    return "sgemm_ws_kernel.cuh" if v[13] == 1 else "sgemm_kernel.cuh"
+
+
+def kernel_name(v: tuple) -> str:
+    return "sgemm_ws_kernel" if v[13] == 1 else "sgemm_kernel"
 
 
 def generate(config_file, out_dir, extra_pairs=None):
@@ -160,13 +181,13 @@ def generate(config_file, out_dir, extra_pairs=None):
         code = f"""// Generated by rocm_sgemm_b200/config/generate_config.py - do not edit.
 // variant {vi}: {dict(zip(VARIANT_FIELDS, variants[vi]))}
 // layout A={'row col'.split()[a]} B={'row col'.split()[b]} C={'row col'.split()[c]}
-#include "../sgemm_kernel.cuh"
+#include "../{kernel_header(variants[vi])}"
 
 namespace sgemm_b200
 {{
 using Cfg = {cfg_type(variants[vi])};
-const void* kernel_v{vi}_{ls}_aligned() {{ return reinterpret_cast<const void*>(&sgemm_kernel<Cfg, {a}, {b}, {c}, true>); }}
-const void* kernel_v{vi}_{ls}_unaligned() {{ return reinterpret_cast<const void*>(&sgemm_kernel<Cfg, {a}, {b}, {c}, false>); }}
+const void* kernel_v{vi}_{ls}_aligned() {{ return reinterpret_cast<const void*>(&{kernel_name(variants[vi])}<Cfg, {a}, {b}, {c}, true>); }}
+const void* kernel_v{vi}_{ls}_unaligned() {{ return reinterpret_cast<const void*>(&{kernel_name(variants[vi])}<Cfg, {a}, {b}, {c}, false>); }}
 }} // namespace sgemm_b200
 """
         (out / name).write_text(code)

@@ -25,7 +25,7 @@ struct KernelVariant
 {
     int block_size, block_m, block_n, block_k;
     int warp_tile_m_count, warp_tile_n_count, thread_tile_m, thread_tile_n, threads_n;
-    int stages, fma_mode, raster, min_blocks;
+    int stages, fma_mode, raster, min_blocks, pipeline;
 };
 
 struct ConfigKey

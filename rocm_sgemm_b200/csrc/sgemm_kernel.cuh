@@ -294,6 +294,104 @@ __device__ __forceinline__ void map_tile(int tile_id, int grid_m, int grid_n, in
 }
 
 // ------------------------------------------------------------------------------------------------
+// register tile -> global C.  (m_base, n_base) is the first row / column this thread owns; its
+// sub-tiles repeat every SUB_M rows and SUB_N columns.  128-bit stores along C's contiguous dimension
+// (the reference stores scalars: kernel/kernel.hpp:299-361); guarded unless ALIGNED.
+// ------------------------------------------------------------------------------------------------
+template<class Cfg, int LC, bool ALIGNED>
+__device__ __forceinline__ void store_tile(const float (&c)[Cfg::TMT][Cfg::TNT], const GemmArgs& p,
+                                           float* __restrict__ out, int m_base, int n_base)
+{
+    constexpr int TM = Cfg::TM, TN = Cfg::TN;
+    if constexpr(LC == LAYOUT_ROW)
+    {
+#pragma unroll
+        for(int im = 0; im < Cfg::WM_CNT; ++im)
+#pragma unroll
+            for(int ii = 0; ii < TM; ++ii)
+            {
+                const int i = im * TM + ii;
+                const int m = m_base + im * Cfg::SUB_M + ii;
+#pragma unroll
+                for(int in = 0; in < Cfg::WN_CNT; ++in)
+                {
+                    const int n   = n_base + in * Cfg::SUB_N;
+                    float*    dst = out + (long long)m * p.ldc + n;
+                    if constexpr(ALIGNED && TN % 4 == 0)
+                    {
+#pragma unroll
+                        for(int v = 0; v < TN / 4; ++v)
+                            *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
+                                c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1], c[i][in * TN + 4 * v + 2],
+                                c[i][in * TN + 4 * v + 3]);
+                    }
+                    else if(m < p.M)
+                    {
+                        if(TN % 4 == 0 && p.vec_c && n + TN <= p.N)
+                        {
+#pragma unroll
+                            for(int v = 0; v < TN / 4; ++v)
+                                *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
+                                    c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1], c[i][in * TN + 4 * v + 2],
+                                    c[i][in * TN + 4 * v + 3]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for(int jj = 0; jj < TN; ++jj)
+                                if(n + jj < p.N)
+                                    dst[jj] = c[i][in * TN + jj];
+                        }
+                    }
+                }
+            }
+    }
+    else
+    {
+#pragma unroll
+        for(int in = 0; in < Cfg::WN_CNT; ++in)
+#pragma unroll
+            for(int jj = 0; jj < TN; ++jj)
+            {
+                const int j = in * TN + jj;
+                const int n = n_base + in * Cfg::SUB_N + jj;
+#pragma unroll
+                for(int im = 0; im < Cfg::WM_CNT; ++im)
+                {
+                    const int m   = m_base + im * Cfg::SUB_M;
+                    float*    dst = out + (long long)n * p.ldc + m;
+                    if constexpr(ALIGNED && TM % 4 == 0)
+                    {
+#pragma unroll
+                        for(int v = 0; v < TM / 4; ++v)
+                            *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
+                                c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j], c[im * TM + 4 * v + 2][j],
+                                c[im * TM + 4 * v + 3][j]);
+                    }
+                    else if(n < p.N)
+                    {
+                        if(TM % 4 == 0 && p.vec_c && m + TM <= p.M)
+                        {
+#pragma unroll
+                            for(int v = 0; v < TM / 4; ++v)
+                                *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
+                                    c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j], c[im * TM + 4 * v + 2][j],
+                                    c[im * TM + 4 * v + 3][j]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for(int ii = 0; ii < TM; ++ii)
+                                if(m + ii < p.M)
+                                    dst[ii] = c[im * TM + ii][j];
+                        }
+                    }
+                }
+            }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------------------
 template<class Cfg, int LA, int LB, int LC, bool ALIGNED>
@@ -560,92 +658,7 @@ __global__ void __launch_bounds__(Cfg::BLOCK_SIZE, Cfg::MIN_BLOCKS) sgemm_kernel
     }
 
     float* __restrict__ out = p.C + (long long)split * p.split_stride;
-    if constexpr(LC == LAYOUT_ROW)
-    {
-#pragma unroll
-        for(int im = 0; im < Cfg::WM_CNT; ++im)
-#pragma unroll
-            for(int ii = 0; ii < TM; ++ii)
-            {
-                const int i = im * TM + ii;
-                const int m = m0 + tm0 + im * Cfg::SUB_M + ii;
-#pragma unroll
-                for(int in = 0; in < Cfg::WN_CNT; ++in)
-                {
-                    const int n   = n0 + tn0 + in * Cfg::SUB_N;
-                    float*    dst = out + (long long)m * p.ldc + n;
-                    if constexpr(ALIGNED && TN % 4 == 0)
-                    {
-#pragma unroll
-                        for(int v = 0; v < TN / 4; ++v)
-                            *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1], c[i][in * TN + 4 * v + 2],
-                                c[i][in * TN + 4 * v + 3]);
-                    }
-                    else if(m < p.M)
-                    {
-                        if(TN % 4 == 0 && p.vec_c && n + TN <= p.N)
-                        {
-#pragma unroll
-                            for(int v = 0; v < TN / 4; ++v)
-                                *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                    c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1], c[i][in * TN + 4 * v + 2],
-                                    c[i][in * TN + 4 * v + 3]);
-                        }
-                        else
-                        {
-#pragma unroll
-                            for(int jj = 0; jj < TN; ++jj)
-                                if(n + jj < p.N)
-                                    dst[jj] = c[i][in * TN + jj];
-                        }
-                    }
-                }
-            }
-    }
-    else
-    {
-#pragma unroll
-        for(int in = 0; in < Cfg::WN_CNT; ++in)
-#pragma unroll
-            for(int jj = 0; jj < TN; ++jj)
-            {
-                const int j = in * TN + jj;
-                const int n = n0 + tn0 + in * Cfg::SUB_N + jj;
-#pragma unroll
-                for(int im = 0; im < Cfg::WM_CNT; ++im)
-                {
-                    const int m   = m0 + tm0 + im * Cfg::SUB_M;
-                    float*    dst = out + (long long)n * p.ldc + m;
-                    if constexpr(ALIGNED && TM % 4 == 0)
-                    {
-#pragma unroll
-                        for(int v = 0; v < TM / 4; ++v)
-                            *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j], c[im * TM + 4 * v + 2][j],
-                                c[im * TM + 4 * v + 3][j]);
-                    }
-                    else if(n < p.N)
-                    {
-                        if(TM % 4 == 0 && p.vec_c && m + TM <= p.M)
-                        {
-#pragma unroll
-                            for(int v = 0; v < TM / 4; ++v)
-                                *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                    c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j], c[im * TM + 4 * v + 2][j],
-                                    c[im * TM + 4 * v + 3][j]);
-                        }
-                        else
-                        {
-#pragma unroll
-                            for(int ii = 0; ii < TM; ++ii)
-                                if(m + ii < p.M)
-                                    dst[ii] = c[im * TM + ii][j];
-                        }
-                    }
-                }
-            }
-    }
+    store_tile<Cfg, LC, ALIGNED>(c, p, out, m0 + tm0, n0 + tn0);
 }
 
 } // namespace sgemm_b200

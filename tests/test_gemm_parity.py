@@ -319,3 +319,8 @@ def test_fma_probe_runs(sgemm):
     for mode in (0, 1):
         r = sgemm.fma_peak(mode, 512)
         assert r["ms"] > 0 and 1.0 < r["tflops"] < 200.0
+
+
+def test_device_status_clean(sgemm):
+    """No kernel launched by this module gave up a bounded wait."""
+    assert sgemm.device_status() == 0
