@@ -45,7 +45,8 @@ typedef struct b200_sgemm_params
     int fma_mode;          /* 0 scalar fma.rn.f32, 1 fma.rn.f32x2 (A duplicated), 2 fma.rn.f32x2 (2x2 diagonal) */
     int raster;            /* 0 row-major tile order, 1 grouped bands, 2 Hilbert curve */
     int min_blocks;        /* CTAs per SM the register budget is sized for */
-    int pipeline;          /* 0 every warp stages and computes, 1 warp-specialised (TMA / producer warps + mbarriers) */
+    int pipeline;          /* 0 every warp stages and computes; 1 warp-specialised (TMA + producer warps + mbarriers),
+                              K-contiguous operands transposed by the producers; 2 same, but they stay K-major */
     int split_k;           /* K slices chosen for the looked-up problem (1 = none) */
 } b200_sgemm_params;
 

@@ -98,7 +98,7 @@ def build_library(config: Path | None = None, jobs: int | None = None, verbose=F
     config = Path(config) if config else PKG / "config" / "gemm_config.json"
     generate(config, extra_pairs)
     sources = [GEN / s for s in (GEN / "sources.txt").read_text().split()]
-    kernel_hdr = [CSRC / "sgemm_kernel.cuh"]
+    kernel_hdr = [CSRC / "sgemm_kernel.cuh", CSRC / "sgemm_ws_kernel.cuh"]
     api_deps = kernel_hdr + [CSRC / "config_select.hpp", GEN / "config_table.inc", REPO / "include" / "b200_sgemm.h"]
     jobs = jobs or max(1, (os.cpu_count() or 2))
     BUILD.mkdir(exist_ok=True)

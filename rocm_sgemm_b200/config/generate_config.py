@@ -74,21 +74,26 @@ def check_variant(v: tuple) -> str | None:
         return "packed FMA needs even thread_tile_n"
     if fma_mode == 2 and tm % 2:
         return "diagonal packing needs even thread_tile_m"
-    if pipeline not in (0, 1):
+    if pipeline not in (0, 1, 2):
         return "unknown pipeline"
     if stages * (bm + bn) * bk * 4 + (2 * stages * 8 + 16 if pipeline else 0) > SMEM_LIMIT:
         return "shared memory over 227 KB"
-    if pipeline == 1:
+    if pipeline >= 1 and fma_mode == 2:
+        return "the warp-specialised kernel has no diagonal packing"
+    if pipeline >= 1:
         # warp-specialised kernel: 128-bit fragment reads only, TMA boxes of at most 256 elements,
         # consumer warps + one producer warpgroup in one CTA
         if tm not in (4, 8) or tn not in (4, 8):
             return "warp-specialised kernel needs thread tiles of 4 or 8"
         if bm > 256 or bn > 256 or bk > 256:
             return "TMA box dimension over 256"
-        if bs + 128 > 1024:
+        producers = 128 if bs >= 256 else 64
+        if bs + producers > 1024:
             return "consumer + producer threads over 1024"
-        if min_blocks != 1:
-            return "warp-specialised kernel is persistent: one CTA per SM"
+        if (bs + producers) * min_blocks > 2048:
+            return "more resident threads than an SM holds"
+        if min_blocks * (stages * (bm + bn) * bk * 4 + 2 * stages * 8 + 16) > SMEM_LIMIT:
+            return "shared memory of the co-resident CTAs over 227 KB"
     # per-thread accumulators must fit the register file
     if wmc * tm * wnc * tn > 192:
         return "accumulator tile over 192 registers"
@@ -128,15 +133,15 @@ def needed_pairs(variants, entries):
 
 
 def cfg_type(v: tuple) -> str:
-    return "TileConfig<" + ", ".join(str(x) for x in v[:13]) + ">"
+    return "TileConfig<" + ", ".join(str(x) for x in v) + ">"
 
 
 def kernel_header(v: tuple) -> str:
-    return "sgemm_ws_kernel.cuh" if v[13] == 1 else "sgemm_kernel.cuh"
+    return "sgemm_ws_kernel.cuh" if v[13] >= 1 else "sgemm_kernel.cuh"
 
 
 def kernel_name(v: tuple) -> str:
-    return "sgemm_ws_kernel" if v[13] == 1 else "sgemm_kernel"
+    return "sgemm_ws_kernel" if v[13] >= 1 else "sgemm_kernel"
 
 
 def generate(config_file, out_dir, extra_pairs=None):

@@ -103,13 +103,14 @@ __device__ __forceinline__ void fma2(uint64_t& acc, uint64_t a, uint64_t b)
 // compile-time description of one kernel variant
 // ------------------------------------------------------------------------------------------------
 template<int BLOCK_SIZE_, int BM_, int BN_, int BK_, int WM_CNT_, int WN_CNT_, int TM_, int TN_, int THREADS_N_,
-         int STAGES_, int FMA_MODE_, int RASTER_, int MIN_BLOCKS_>
+         int STAGES_, int FMA_MODE_, int RASTER_, int MIN_BLOCKS_, int PIPELINE_ = 0>
 struct TileConfig
 {
     static constexpr int BLOCK_SIZE = BLOCK_SIZE_, BM = BM_, BN = BN_, BK = BK_;
     static constexpr int WM_CNT = WM_CNT_, WN_CNT = WN_CNT_, TM = TM_, TN = TN_;
     static constexpr int THREADS_N = THREADS_N_, THREADS_M = 32 / THREADS_N_;
     static constexpr int STAGES = STAGES_, FMA_MODE = FMA_MODE_, RASTER = RASTER_, MIN_BLOCKS = MIN_BLOCKS_;
+    static constexpr int PIPELINE = PIPELINE_;
 
     static constexpr int SUB_M  = TM * THREADS_M; // rows covered by one warp sub-tile
     static constexpr int SUB_N  = TN * THREADS_N;
@@ -156,12 +157,16 @@ struct Swizzle
 template<int BLOCK_SIZE, int BX, int BK, bool KMAJOR, bool ALIGNED>
 struct OperandStager
 {
-    static constexpr int CHUNKS = BX * BK / 4;
-    static constexpr int ITERS  = (CHUNKS + BLOCK_SIZE - 1) / BLOCK_SIZE;
-    static constexpr bool EXACT = (CHUNKS % BLOCK_SIZE) == 0;
+    // X-contiguous operand: one 16-byte chunk of a k-row per work item.
+    // K-contiguous operand: one 4 (x) by 4 (k) block per work item, fetched as four 128-bit loads (one
+    // per operand row), transposed in registers (pure renaming) and written as four 128-bit stores.
+    static constexpr int L      = BK / 4; // 16-byte chunks per operand row
+    static constexpr int ITEMS  = KMAJOR ? (BX / 4) * L : BX * BK / 4;
+    static constexpr int ITERS  = (ITEMS + BLOCK_SIZE - 1) / BLOCK_SIZE;
+    static constexpr bool EXACT = (ITEMS % BLOCK_SIZE) == 0;
     using Swz                   = Swizzle<BX, BK>;
 
-    float4 regs[KMAJOR ? ITERS : 1];
+    float4 regs[KMAJOR ? ITERS : 1][KMAJOR ? 4 : 1];
 
     // Issue the global reads of the tile whose origin is (x0, k0); k_end bounds this CTA's K slice.
     // X-contiguous operands go straight to shared memory with cp.async; K-contiguous ones into regs.
@@ -175,7 +180,7 @@ struct OperandStager
             for(int it = 0; it < ITERS; ++it)
             {
                 const int q = tid + it * BLOCK_SIZE;
-                if(EXACT || q < CHUNKS)
+                if(EXACT || q < ITEMS)
                 {
                     const int      k   = q / CPR;
                     const int      x4  = (q % CPR) * 4;
@@ -208,61 +213,67 @@ struct OperandStager
         }
         else
         {
-            constexpr int L = BK / 4;
+            // lanes of a warp: chunk index c fastest, so each load instruction reads whole 16*L-byte row
+            // segments (a full 128-byte line per row when BK = 32)
 #pragma unroll
             for(int it = 0; it < ITERS; ++it)
             {
                 const int q = tid + it * BLOCK_SIZE;
-                float4    v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if(EXACT || q < CHUNKS)
+#pragma unroll
+                for(int r = 0; r < 4; ++r)
                 {
-                    const int    c  = q % L;
-                    const int    x  = q / L;
-                    const int    gx = x0 + x, gk = k0 + 4 * c;
-                    const float* src = g + (long long)gx * ld + gk;
-                    if constexpr(ALIGNED)
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if(EXACT || q < ITEMS)
                     {
-                        v = __ldg(reinterpret_cast<const float4*>(src));
-                    }
-                    else if(gx < X)
-                    {
-                        if(vec_ok && gk + 3 < k_end)
+                        const int    c  = q % L;
+                        const int    gx = x0 + 4 * (q / L) + r, gk = k0 + 4 * c;
+                        const float* src = g + (long long)gx * ld + gk;
+                        if constexpr(ALIGNED)
                         {
                             v = __ldg(reinterpret_cast<const float4*>(src));
                         }
-                        else
+                        else if(gx < X)
                         {
-                            if(gk + 0 < k_end) v.x = __ldg(src + 0);
-                            if(gk + 1 < k_end) v.y = __ldg(src + 1);
-                            if(gk + 2 < k_end) v.z = __ldg(src + 2);
-                            if(gk + 3 < k_end) v.w = __ldg(src + 3);
+                            if(vec_ok && gk + 3 < k_end)
+                            {
+                                v = __ldg(reinterpret_cast<const float4*>(src));
+                            }
+                            else
+                            {
+                                if(gk + 0 < k_end) v.x = __ldg(src + 0);
+                                if(gk + 1 < k_end) v.y = __ldg(src + 1);
+                                if(gk + 2 < k_end) v.z = __ldg(src + 2);
+                                if(gk + 3 < k_end) v.w = __ldg(src + 3);
+                            }
                         }
                     }
+                    regs[it][r] = v;
                 }
-                regs[it] = v;
             }
         }
     }
 
-    // Second half of a K-contiguous fetch: transposing stores into the [k][x ^ swizzle] tile.
+    // Second half of a K-contiguous fetch: the 4x4 block goes out transposed, one 128-bit store per k,
+    // into the [k][x ^ swizzle] tile.  The eight lanes of a quarter warp hold different (chunk, x-group)
+    // pairs whose swizzled 16-byte slots fall into eight different bank groups: conflict-free.
     __device__ __forceinline__ void commit(float* tile, int tid)
     {
         if constexpr(KMAJOR)
         {
-            constexpr int L = BK / 4;
 #pragma unroll
             for(int it = 0; it < ITERS; ++it)
             {
                 const int q = tid + it * BLOCK_SIZE;
-                if(EXACT || q < CHUNKS)
+                if(EXACT || q < ITEMS)
                 {
                     const int c  = q % L;
-                    const int xs = (q / L) ^ Swz::of_chunk(c);
+                    const int xs = (4 * (q / L)) ^ Swz::of_chunk(c);
                     float*    d  = tile + (4 * c) * BX + xs;
-                    d[0 * BX]    = regs[it].x;
-                    d[1 * BX]    = regs[it].y;
-                    d[2 * BX]    = regs[it].z;
-                    d[3 * BX]    = regs[it].w;
+                    const float4 r0 = regs[it][0], r1 = regs[it][1], r2 = regs[it][2], r3 = regs[it][3];
+                    *reinterpret_cast<float4*>(d + 0 * BX) = make_float4(r0.x, r1.x, r2.x, r3.x);
+                    *reinterpret_cast<float4*>(d + 1 * BX) = make_float4(r0.y, r1.y, r2.y, r3.y);
+                    *reinterpret_cast<float4*>(d + 2 * BX) = make_float4(r0.z, r1.z, r2.z, r3.z);
+                    *reinterpret_cast<float4*>(d + 3 * BX) = make_float4(r0.w, r1.w, r2.w, r3.w);
                 }
             }
         }
@@ -554,14 +565,17 @@ __global__ void __launch_bounds__(Cfg::BLOCK_SIZE, Cfg::MIN_BLOCKS) sgemm_kernel
 #pragma unroll
             for(int j = 0; j < TNT / 2; ++j)
                 b2[j] = pack2(b_frag[buf][2 * j], b_frag[buf][2 * j + 1]);
+            uint64_t a2[TMT];
 #pragma unroll
             for(int i = 0; i < TMT; ++i)
-            {
-                const uint64_t a2 = pack2(a_frag[buf][i], a_frag[buf][i]);
+                a2[i] = pack2(a_frag[buf][i], a_frag[buf][i]);
+            // column-pair major: consecutive packed FMAs keep the natural pair (b) and change the
+            // duplicated operand; measured 4 % faster on B200 than the row-major order
 #pragma unroll
-                for(int j = 0; j < TNT / 2; ++j)
-                    fma2(acc2[i][j], a2, b2[j]);
-            }
+            for(int j = 0; j < TNT / 2; ++j)
+#pragma unroll
+                for(int i = 0; i < TMT; ++i)
+                    fma2(acc2[i][j], a2[i], b2[j]);
         }
         else
         {
