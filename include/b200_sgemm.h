@@ -27,6 +27,7 @@ extern "C" {
 #define B200_SGEMM_NO_KERNEL (-2)        /* no kernel built for (variant, layout, alignment) */
 #define B200_SGEMM_WORKSPACE_TOO_SMALL (-3)
 #define B200_SGEMM_UNSUPPORTED_SIZE (-4) /* a dimension exceeds what the kernels index (2^31-1) */
+#define B200_SGEMM_SCRATCH_LIMIT (-5)    /* b200_sgemm_splitk_static: split_k * M * N floats exceed the built-in scratch */
 
 /* Tile parameters of one kernel variant: the reference's nine (struct gemm_params emitted by
  * rocm_sgemm/config/generate_config.py:100-111) followed by the CUDA-side additions. */
@@ -112,6 +113,24 @@ int b200_sgemm_fma_peak(int mode, int iterations, float* elapsed_ms, double* flo
  * shared-memory barrier (consumer / producer side) and its output is invalid.  Diagnostic only: the
  * reference has no counterpart because its kernel has no waits that could time out. */
 int b200_sgemm_device_status(int* status);
+
+/* Size of the scratch array that b200_sgemm_splitk_static uses; it is part of the library image. */
+#define B200_SGEMM_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+/* Split-K GEMM for callers that cannot allocate device memory and cannot pass a workspace: hosts whose
+ * memory pool already owns the whole device, latency-bound threads that must stay out of the driver's
+ * allocator, plug-ins barred from allocating after their init hook.  Same operation and arguments as
+ * b200_sgemm plus the number of K slices (>= 2); the partial sums live in a fixed
+ * B200_SGEMM_STATIC_SCRATCH_BYTES array inside the library, which every GPU that loads the library
+ * holds until the process exits.  The call allocates nothing.  split_k * M * N * 4 bytes must fit the
+ * array, else B200_SGEMM_SCRATCH_LIMIT is returned and nothing runs.  The first call on a device
+ * resolves the array's device address; make that call before any stream capture on the device.  All
+ * calls share the array (it keeps the previous call's contents; no part of it needs clearing because
+ * every slice is fully written before it is read), so calls that can overlap on the GPU race: keep them
+ * on one stream or order them with events.
+ * This entry point has no counterpart in the reference, whose kernel needs no scratch memory. */
+int b200_sgemm_splitk_static(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
+                             size_t M, size_t N, size_t K, int split_k, void* cuda_stream);
 
 /* Frees the internal split-K arenas of every device (optional; they are also freed at unload). */
 int b200_sgemm_shutdown(void);

@@ -36,6 +36,8 @@ INVALID_ARGUMENT = -1
 NO_KERNEL = -2
 WORKSPACE_TOO_SMALL = -3
 UNSUPPORTED_SIZE = -4
+SCRATCH_LIMIT = -5
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 
 class _Params(ctypes.Structure):
@@ -81,7 +83,7 @@ _vp = ctypes.c_void_p
 EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sgemm_select_config",
            "b200_sgemm_num_variants", "b200_sgemm_get_variant", "b200_sgemm_num_entries", "b200_sgemm_get_entry",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
-           "b200_sgemm_shutdown",
+           "b200_sgemm_splitk_static", "b200_sgemm_shutdown",
            "b200_sgemm_status_string")
 
 
@@ -107,6 +109,7 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_select_in_table.argtypes = [ctypes.POINTER(_sz), _sz, _sz, _sz, _sz, i, i, i]
     l.b200_sgemm_fma_peak.argtypes = [i, i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double), _vp]
     l.b200_sgemm_device_status.argtypes = [ctypes.POINTER(i)]
+    l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
     _lib = l
@@ -162,6 +165,14 @@ def gemm_ex(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, lda: 
     """The explicit form: leading dimensions (0 = packed), forced variant / split-K, caller workspace."""
     _check(lib().b200_sgemm_ex(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K, lda,
                                ldb, ldc, variant, split_k, _ptr(workspace), workspace_bytes, _stream(stream)))
+
+
+def gemm_splitk_static(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, split_k: int, stream=None) -> None:
+    """Split-K GEMM whose partial sums live in the library's built-in 32 MiB device array: for callers
+    that may not allocate device memory.  Raises SgemmError(SCRATCH_LIMIT) when split_k*M*N floats do not
+    fit.  Calls on one device share the array: do not let two of them overlap on the GPU."""
+    _check(lib().b200_sgemm_splitk_static(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M,
+                                          N, K, split_k, _stream(stream)))
 
 
 def workspace_bytes(layout_c, layout_a, layout_b, M, N, K, variant: int = -1, split_k: int = 0) -> int:
