@@ -46,9 +46,9 @@ typedef struct b200_sgemm_params
     int fma_mode;          /* 0 scalar fma.rn.f32, 1 fma.rn.f32x2 (A duplicated), 2 fma.rn.f32x2 (2x2 diagonal) */
     int raster;            /* 0 row-major tile order, 1 grouped bands, 2 Hilbert curve */
     int min_blocks;        /* CTAs per SM the register budget is sized for */
-    int pipeline;          /* 0 every warp stages and computes; 1 warp-specialised (TMA + producer warps + mbarriers),
-                              K-contiguous operands transposed by the producers; 2 same, but they stay K-major */
+    int pipeline;          /* 0 every warp stages and computes, 1 warp-specialised (TMA / producer warps + mbarriers) */
     int split_k;           /* K slices chosen for the looked-up problem (1 = none) */
+    int pretranspose;      /* bit 0 / 1: b200_sgemm first copies a K-contiguous A / B into M / N-contiguous scratch */
 } b200_sgemm_params;
 
 /* C = A*B, C overwritten, packed matrices, asynchronous on `cuda_stream` (a cudaStream_t; NULL = the
@@ -57,7 +57,11 @@ typedef struct b200_sgemm_params
  * (rocm_sgemm/include/rocm_sgemm/gemm.hpp:51-52, rocm_sgemm/src/gemm.cpp:8-41): same argument order
  * (C, A, B), same semantics (alpha = 1, beta = 0, inputs untouched), additionally correct for ragged
  * M, N, K.  A is MxK, B is KxN, C is MxN.  When the tuned table asks for split-K the library takes
- * the partial-sum buffer from an internal per-(device, stream) arena that grows on demand. */
+ * the partial-sum buffer from an internal per-(device, stream) arena that grows on demand.  Where the
+ * table allows it and the problem is large enough for it to pay (the other dimension >= 1024), a
+ * K-contiguous operand (row-major A, col-major B) is first copied transposed into the same arena, so
+ * that the hot kernel can fetch it with TMA: about 1 % extra time at 4096^3 instead of 5 % lost to
+ * transposition inside the kernel.  b200_sgemm_ex never does this: it runs exactly the kernel it is told. */
 int b200_sgemm(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M, size_t N,
                size_t K, void* cuda_stream);
 
@@ -92,6 +96,7 @@ int b200_sgemm_get_variant(int variant, b200_sgemm_params* out);
  * mnk = {M, N, K}; layouts = {A, B, C}. */
 int b200_sgemm_num_entries(void);
 int b200_sgemm_get_entry(int index, size_t mnk[3], int layouts[3], int* variant, int* split_k);
+int b200_sgemm_get_entry_pretranspose(int index); /* the entry's pretranspose bits, or -1 */
 
 /* 1 when a kernel exists for (variant, layout index A*4+B*2+C, aligned 0/1), as a non-null
  * kernel_table slot does in the reference (rocm_sgemm/include/rocm_sgemm/kernel_lookup.hpp:39). */

@@ -49,6 +49,7 @@ struct gemm_params
     int min_blocks;
     int pipeline;
     int split_k;
+    int pretranspose;
 };
 
 inline gemm_params get_gemm_params(size_t m, size_t n, size_t k, m_layout layout_c, m_layout layout_a,
@@ -61,7 +62,8 @@ inline gemm_params get_gemm_params(size_t m, size_t n, size_t k, m_layout layout
         throw std::runtime_error(std::string("rocm_sgemm::get_gemm_params: ") + b200_sgemm_status_string(status));
     return gemm_params{p.block_size, p.block_m,       p.block_n,       p.block_k,   p.warp_tile_m_count,
                        p.warp_tile_n_count, p.thread_tile_m, p.thread_tile_n, p.threads_n, p.stages,
-                       p.fma_mode,   p.raster,        p.min_blocks,    p.pipeline,  p.split_k};
+                       p.fma_mode,   p.raster,        p.min_blocks,    p.pipeline,  p.split_k,
+                       p.pretranspose};
 }
 
 /// Number of kernel variants built into the library (the reference's constant KERNEL_VARIANTS).

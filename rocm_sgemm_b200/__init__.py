@@ -43,7 +43,7 @@ STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 class _Params(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in (
         "block_size", "block_m", "block_n", "block_k", "warp_tile_m_count", "warp_tile_n_count", "thread_tile_m",
-        "thread_tile_n", "threads_n", "stages", "fma_mode", "raster", "min_blocks", "pipeline", "split_k")]
+        "thread_tile_n", "threads_n", "stages", "fma_mode", "raster", "min_blocks", "pipeline", "split_k", "pretranspose")]
 
 
 @dataclass(frozen=True)
@@ -64,6 +64,7 @@ class gemm_params:
     min_blocks: int
     pipeline: int
     split_k: int
+    pretranspose: int
 
     def nine(self) -> tuple:
         return (self.block_size, self.block_m, self.block_n, self.block_k, self.warp_tile_m_count,
@@ -82,6 +83,7 @@ _vp = ctypes.c_void_p
 
 EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sgemm_select_config",
            "b200_sgemm_num_variants", "b200_sgemm_get_variant", "b200_sgemm_num_entries", "b200_sgemm_get_entry",
+           "b200_sgemm_get_entry_pretranspose",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
            "b200_sgemm_splitk_static", "b200_sgemm_shutdown",
            "b200_sgemm_status_string")

@@ -139,7 +139,7 @@ def build_harness(verbose=False):
             continue
         deps = [p for p in hdir.glob("*.hpp")] + [REPO / "include" / "rocm_sgemm" / "gemm.hpp",
                                                   REPO / "include" / "b200_sgemm.h"]
-        flags = NVCC_FLAGS + ["-I", str(REPO / "include"), "-I", str(hdir)]
+        flags = NVCC_FLAGS + ["-I", str(REPO / "include"), "-I", str(hdir), "-Xcompiler", "-fopenmp"]
         obj = _compile(src, deps, flags, verbose)
         exe = BIN / name
         cmd = [nvcc()] + ARCH_FLAGS + ["-o", str(exe), str(obj), "-L", str(PKG), "-lb200_sgemm",

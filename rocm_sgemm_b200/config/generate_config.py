@@ -4,8 +4,8 @@
 Input: the tuned table `gemm_config.json` — the schema of the reference's
 rocm_sgemm/config/gemm_config.json (a list of {range{M,N,K}, layout{A,B,C}, config{...}}) whose
 `config` block carries the reference's nine tile parameters plus the optional CUDA-side knobs
-`stages`, `fma_mode`, `raster`, `min_blocks` (kernel-variant properties) and `split_k` (a property of
-the table entry).
+`stages`, `fma_mode`, `raster`, `min_blocks`, `pipeline` (kernel-variant properties) and `split_k`,
+`pretranspose` (properties of the table entry).
 
 Output, into one directory (the role of rocm_sgemm/config/generate_config.py:7-545):
   config_table.inc        kernel-variant array + sorted (M,N,K,A,B,C) -> (variant, split_k) map
@@ -74,7 +74,7 @@ def check_variant(v: tuple) -> str | None:
         return "packed FMA needs even thread_tile_n"
     if fma_mode == 2 and tm % 2:
         return "diagonal packing needs even thread_tile_m"
-    if pipeline not in (0, 1, 2):
+    if pipeline not in (0, 1):
         return "unknown pipeline"
     if stages * (bm + bn) * bk * 4 + (2 * stages * 8 + 16 if pipeline else 0) > SMEM_LIMIT:
         return "shared memory over 227 KB"
@@ -117,15 +117,22 @@ def load_table(config_file, extra_variants=()):
     for conf in table["configurations"]:
         r, l = conf["range"], conf["layout"]
         key = (int(r["M"]), int(r["N"]), int(r["K"]), LAYOUT_VAL[l["A"]], LAYOUT_VAL[l["B"]], LAYOUT_VAL[l["C"]])
-        entries[key] = (variants.index(variant_of(conf["config"])), int(conf["config"].get("split_k", 1)))
+        entries[key] = (variants.index(variant_of(conf["config"])), int(conf["config"].get("split_k", 1)),
+                        int(conf["config"].get("pretranspose", 0)))
     entries = sorted(entries.items())  # by (M, N, K, A, B, C): the order the lookup's binary search needs
     return variants, entries
 
 
 def needed_pairs(variants, entries):
     pairs = set()
-    for key, (vi, _) in entries:
-        pairs.add((vi, key[3:6]))
+    for key, (vi, _, pre) in entries:
+        a, b, c = key[3:6]
+        pairs.add((vi, (a, b, c)))
+        # a pre-transposed K-contiguous operand is handed to the kernel as an M / N-contiguous one
+        if pre:
+            pairs.add((vi, (1 if (pre & 1) else a, 0 if (pre & 2) else b, c)))
+            pairs.add((vi, (1 if (pre & 1) else a, b, c)))
+            pairs.add((vi, (a, 0 if (pre & 2) else b, c)))
     d = variants.index(DEFAULT_VARIANT)
     for lay in LAYOUTS:
         pairs.add((d, lay))
@@ -170,11 +177,11 @@ def generate(config_file, out_dir, extra_pairs=None):
     lines.append("};")
     lines.append(f"static constexpr int CONFIG_ENTRIES = {len(entries)};")
     lines.append(f"static const ConfigEntry sorted_config_map[{max(1, len(entries))}] = {{")
-    for key, (vi, sk) in entries:
+    for key, (vi, sk, pre) in entries:
         m, n, k, a, b, c = key
-        lines.append(f"    {{{{{m}, {n}, {k}, {a}, {b}, {c}}}, {vi}, {sk}}}, // {m}x{n}x{k} {layout_str(a, b, c)}")
+        lines.append(f"    {{{{{m}, {n}, {k}, {a}, {b}, {c}}}, {vi}, {sk}, {pre}}}, // {m}x{n}x{k} {layout_str(a, b, c)}")
     if not entries:
-        lines.append("    {{0, 0, 0, 0, 0, 0}, 0, 1}")
+        lines.append("    {{0, 0, 0, 0, 0, 0}, 0, 1, 0}")
     lines.append("};")
     (out / "config_table.inc").write_text("\n".join(lines) + "\n")
 

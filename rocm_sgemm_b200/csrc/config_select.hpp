@@ -54,6 +54,7 @@ struct ConfigEntry
     ConfigKey key;
     int       variant; // index into the kernel-variant array
     int       split_k; // K slices tuned for this problem (1 = none)
+    int       pretranspose = 0; // bit 0 / 1: copy a K-contiguous A / B into M / N-contiguous scratch first
 };
 
 inline double config_distance(const ConfigKey& a, const ConfigKey& b)

@@ -96,7 +96,8 @@ def test_generator_output(tmp_path):
     p.write_text(json.dumps(cfg))
     variants, entries, pairs = g.generate(str(p), str(tmp_path / "gen"))
     assert g.DEFAULT_VARIANT in variants and len(variants) == 2
-    assert entries == [((512, 512, 512, 1, 0, 0), (variants.index((128, 64, 128, 8, 2, 2, 4, 4, 8, 2, 2, 1, 1, 0)), 2))]
+    # (variant index, split_k, pretranspose)
+    assert entries == [((512, 512, 512, 1, 0, 0), (variants.index((128, 64, 128, 8, 2, 2, 4, 4, 8, 2, 2, 1, 1, 0)), 2, 0))]
     # the tabled pair plus the default variant in all eight layouts
     assert len(pairs) == 9
     names = (tmp_path / "gen" / "sources.txt").read_text().split()

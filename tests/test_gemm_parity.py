@@ -181,8 +181,9 @@ def test_config5_16384_single_gpu(sgemm, orc):
 # ------------------------------------------------------------------------------------------------
 # ragged and degenerate shapes (the reference's loads are unguarded there; this library is exact)
 # ------------------------------------------------------------------------------------------------
+# the last three are large enough in M or N for the drop-in entry to pre-transpose a K-contiguous operand
 RAGGED = [(1, 1, 1), (3, 5, 7), (1, 300, 40), (300, 1, 40), (127, 129, 65), (130, 70, 33), (257, 255, 100),
-          (33, 1000, 17), (64, 64, 1), (200, 136, 132)]
+          (33, 1000, 17), (64, 64, 1), (200, 136, 132), (130, 1101, 70), (1101, 130, 70), (1027, 1030, 37)]
 
 
 @pytest.mark.parametrize("layout", LAYOUTS, ids=lambda l: layout_name(*l))
