@@ -249,18 +249,16 @@ def ours(args, w):
         dA = torch.from_numpy(hA).to(dev)
         dBfull = torch.from_numpy(hBfull).to(dev)
     if G > 1:
-        # packed K x Nl slice (row-major B: a strided column block made contiguous; col-major: a contiguous range)
-        if lb == 0:
-            dB = dBfull.view(K, N)[:, rank * Nl:(rank + 1) * Nl].contiguous().view(-1)
-        else:
-            dB = dBfull.view(N, K)[rank * Nl:(rank + 1) * Nl].contiguous().view(-1)
+        from rocm_sgemm_b200 import sharded
+        dB = sharded.local_b_slice(dBfull, lb, K, N, G, rank)  # packed K x Nl slice of this rank
         del dBfull
     else:
         dB = dBfull
     dC = torch.empty(M * Nl, dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream()
     params, variant = sg.select_config(M, Nl, K, lc, la, lb)
-    launches_per_step = 2 if params.split_k > 1 else 1
+    # GEMM kernel + split-K reduction + one transposition kernel per pre-transposed operand
+    launches_per_step = 1 + (1 if params.split_k > 1 else 0) + bin(params.pretranspose).count("1")
 
     def step():
         sg.gemm(lc, la, lb, dC, dA, dB, M, Nl, K, stream=stream)

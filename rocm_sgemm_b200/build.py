@@ -149,6 +149,20 @@ def build_harness(verbose=False):
         if r.returncode != 0:
             raise RuntimeError(f"link failed for {name}:\n{r.stderr[-4000:]}")
         outs.append(exe)
+    # the tuner's one-trial executable (loads a candidate build of the library with dlopen)
+    tsrc = PKG / "config" / "tuner.cpp"
+    if tsrc.exists():
+        exe = BIN / "tuner"
+        tag = BIN / f".tuner.{_digest([tsrc, REPO / 'include' / 'b200_sgemm.h'], [])}"
+        if not (exe.exists() and tag.exists()):
+            for old in BIN.glob(".tuner.*"):
+                old.unlink()
+            cmd = [nvcc(), "-O2", "-std=c++17", str(tsrc), "-o", str(exe), "-ldl"]
+            r = subprocess.run(cmd, capture_output=True, text=True, env=_env())
+            if r.returncode != 0:
+                raise RuntimeError(f"tuner build failed:\n{r.stderr[-4000:]}")
+            tag.touch()
+        outs.append(exe)
     return outs
 
 
