@@ -102,6 +102,12 @@ int b200_sgemm_get_entry_pretranspose(int index); /* the entry's pretranspose bi
  * kernel_table slot does in the reference (rocm_sgemm/include/rocm_sgemm/kernel_lookup.hpp:39). */
 int b200_sgemm_has_kernel(int variant, int layout_index, int aligned);
 
+/* Tile order of a kernel variant's `raster` mode: position `id` (0 <= id < grid_m * grid_n) in the order
+ * the CTAs walk the tile grid -> tile coordinates.  0 row-major, 1 bands of eight tile rows, 2 Hilbert
+ * curve.  Host-side evaluation of the kernels' own mapping function (the reference's tile_mapper,
+ * rocm_sgemm/include/rocm_sgemm/kernel/mapping.hpp:211-237, is device-only). */
+int b200_sgemm_map_tile(int raster, int id, int grid_m, int grid_n, int* tile_m, int* tile_n);
+
 /* The selection rule applied to a caller-supplied table (host only, no CUDA): `keys` holds `count`
  * rows of {m, n, k, layout_a, layout_b, layout_c} sorted the way the reference sorts them.
  * Returns the chosen row or -1 for an empty table. */

@@ -83,7 +83,7 @@ _vp = ctypes.c_void_p
 
 EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sgemm_select_config",
            "b200_sgemm_num_variants", "b200_sgemm_get_variant", "b200_sgemm_num_entries", "b200_sgemm_get_entry",
-           "b200_sgemm_get_entry_pretranspose",
+           "b200_sgemm_get_entry_pretranspose", "b200_sgemm_map_tile",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
            "b200_sgemm_splitk_static", "b200_sgemm_shutdown",
            "b200_sgemm_status_string")
@@ -212,6 +212,13 @@ def table_entries() -> list:
         _check(l.b200_sgemm_get_entry(i, mnk, lay, ctypes.byref(v), ctypes.byref(s)))
         out.append((int(mnk[0]), int(mnk[1]), int(mnk[2]), lay[0], lay[1], lay[2], v.value, s.value))
     return out
+
+
+def map_tile(raster: int, tile_id: int, grid_m: int, grid_n: int) -> tuple:
+    """(tile_m, tile_n) of position `tile_id` in the tile order of a raster mode (0 row, 1 bands, 2 Hilbert)."""
+    tm, tn = ctypes.c_int(), ctypes.c_int()
+    _check(lib().b200_sgemm_map_tile(raster, tile_id, grid_m, grid_n, ctypes.byref(tm), ctypes.byref(tn)))
+    return tm.value, tn.value
 
 
 def has_kernel(variant: int, layout_a, layout_b, layout_c, aligned: bool) -> bool:

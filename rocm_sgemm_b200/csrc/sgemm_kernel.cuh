@@ -283,16 +283,122 @@ struct OperandStager
 // ------------------------------------------------------------------------------------------------
 // CTA id -> tile coordinates (the reference's tile_mapper role, kernel/mapping.hpp:211-237)
 // ------------------------------------------------------------------------------------------------
-template<int RASTER>
-__device__ __forceinline__ void map_tile(int tile_id, int grid_m, int grid_n, int& tile_m, int& tile_n)
+// Position d along the Hilbert curve of an s x s square (s a power of two) -> (x, y)
+__host__ __device__ inline void hilbert_d2xy(int s, int d, int& x, int& y)
 {
-    if constexpr(RASTER == RASTER_GROUPED)
+    x = 0;
+    y = 0;
+    int t = d;
+    for(int side = 1; side < s; side <<= 1)
+    {
+        const int rx = 1 & (t >> 1);
+        const int ry = 1 & (t ^ rx);
+        if(ry == 0)
+        {
+            if(rx == 1)
+            {
+                x = side - 1 - x;
+                y = side - 1 - y;
+            }
+            const int tmp = x;
+            x             = y;
+            y             = tmp;
+        }
+        x += side * rx;
+        y += side * ry;
+        t >>= 2;
+    }
+}
+
+// Hilbert order over an arbitrary grid_m x grid_n tile grid: the grid is cut into the largest
+// power-of-two squares that fit along its shorter side (each walked along a Hilbert curve, one after the
+// other along the longer side), and the remaining strips are handled the same way, iteratively.  Tiles
+// that are close in the order are close in both m and n, which keeps the A and B panels of the tiles in
+// flight together small.  (The reference: kernel/mapping.hpp:34-166, Hilbert curve over power-of-two
+// sub-squares with remainder strips; this is an independent formulation.)
+__host__ __device__ inline void hilbert_map(int id, int grid_m, int grid_n, int& tile_m, int& tile_n)
+{
+    int om = 0, on = 0, rows = grid_m, cols = grid_n;
+    for(int guard = 0; guard < 64; ++guard)
+    {
+        const int shorter = rows < cols ? rows : cols;
+        int       s       = 1;
+        while(2 * s <= shorter)
+            s *= 2;
+        const int ss = s * s;
+        if(cols >= rows)
+        {
+            const int nsq = cols / s, count = nsq * ss;
+            if(id < count)
+            {
+                const int sq = id / ss;
+                int       x, y;
+                hilbert_d2xy(s, id - sq * ss, x, y);
+                tile_m = om + y;
+                tile_n = on + sq * s + x;
+                return;
+            }
+            id -= count;
+            const int right = s * (cols - nsq * s); // strip to the right of the squares, s rows tall
+            if(id < right)
+            {
+                on += nsq * s;
+                cols -= nsq * s;
+                rows = s;
+            }
+            else
+            {
+                id -= right;
+                om += s;
+                rows -= s;
+            }
+        }
+        else
+        {
+            const int nsq = rows / s, count = nsq * ss;
+            if(id < count)
+            {
+                const int sq = id / ss;
+                int       x, y;
+                hilbert_d2xy(s, id - sq * ss, x, y);
+                tile_m = om + sq * s + y;
+                tile_n = on + x;
+                return;
+            }
+            id -= count;
+            const int below = s * (rows - nsq * s); // strip below the squares, s columns wide
+            if(id < below)
+            {
+                om += nsq * s;
+                rows -= nsq * s;
+                cols = s;
+            }
+            else
+            {
+                id -= below;
+                on += s;
+                cols -= s;
+            }
+        }
+    }
+    tile_m = 0; // not reached for id < grid_m * grid_n
+    tile_n = 0;
+}
+
+template<int RASTER>
+__host__ __device__ __forceinline__ void map_tile(int tile_id, int grid_m, int grid_n, int& tile_m, int& tile_n)
+{
+    if constexpr(RASTER == RASTER_HILBERT)
+    {
+        hilbert_map(tile_id, grid_m, grid_n, tile_m, tile_n);
+    }
+    else if constexpr(RASTER == RASTER_GROUPED)
     {
         constexpr int GROUP    = 8;
         const int     per_band = GROUP * grid_n;
         const int     band     = tile_id / per_band;
         const int     first_m  = band * GROUP;
-        const int     rows     = min(GROUP, grid_m - first_m);
+        const int     rows     = (GROUP < grid_m - first_m) ? GROUP : grid_m - first_m;
         const int     in_band  = tile_id - band * per_band;
         tile_m                 = first_m + in_band % rows;
         tile_n                 = in_band / rows;
