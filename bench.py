@@ -327,16 +327,16 @@ def ours(args, w):
         hA_t = torch.from_numpy(hA).pin_memory()
         hB_t = dB.cpu().pin_memory()
     hC_t = torch.empty(M * Nl, dtype=torch.float32).pin_memory()
-    dA2, dB2, dC2 = torch.empty_like(dA), torch.empty_like(dB), torch.empty_like(dC)
 
     def e2e_step():
-        dA2.copy_(hA_t, non_blocking=True)
-        dB2.copy_(hB_t, non_blocking=True)
-        sg.gemm(lc, la, lb, dC2, dA2, dB2, M, Nl, K, stream=stream)
-        hC_t.copy_(dC2, non_blocking=True)
+        # one call of the C ABI with HOST buffers: upload, GEMM and download pipelined inside the library
+        sg.gemm_host(lc, la, lb, hC_t, hA_t, hB_t, M, Nl, K)
 
     for _ in range(2):
         e2e_step()
+    if w["init"] == "identity" and G == 1:
+        if not torch.equal(hC_t.view(torch.int32), hA_t.view(torch.int32)):
+            raise SystemExit("host-buffer entry: identity-multiply result differs from A")
     barrier()
     b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     b0.record()

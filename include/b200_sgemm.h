@@ -125,6 +125,16 @@ int b200_sgemm_fma_peak(int mode, int iterations, float* elapsed_ms, double* flo
  * reference has no counterpart because its kernel has no waits that could time out. */
 int b200_sgemm_device_status(int* status);
 
+/* The same operation for matrices in HOST memory: uploads B, then pipelines row panels of A and C
+ * (upload of panel i+1, GEMM of panel i, download of panel i-1 on three streams), and returns when C is
+ * complete in host memory.  This is the sequence the reference's harness performs step by step
+ * (test/gemm/test.cpp:50-74: hipMemcpy H2D, gemm, hipMemcpy D2H) folded into one call; page-locked host
+ * buffers are needed for the overlap.  Device buffers come from a per-device arena of the library
+ * (b200_sgemm_shutdown_host releases it).  Calls are serialised per process. */
+int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
+                    size_t N, size_t K);
+int b200_sgemm_shutdown_host(void);
+
 /* Size of the scratch array that b200_sgemm_splitk_static uses; it is part of the library image. */
 #define B200_SGEMM_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 

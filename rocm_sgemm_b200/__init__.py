@@ -85,7 +85,7 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_num_variants", "b200_sgemm_get_variant", "b200_sgemm_num_entries", "b200_sgemm_get_entry",
            "b200_sgemm_get_entry_pretranspose", "b200_sgemm_map_tile",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
-           "b200_sgemm_splitk_static", "b200_sgemm_shutdown",
+           "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string")
 
 
@@ -111,6 +111,7 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_select_in_table.argtypes = [ctypes.POINTER(_sz), _sz, _sz, _sz, _sz, i, i, i]
     l.b200_sgemm_fma_peak.argtypes = [i, i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double), _vp]
     l.b200_sgemm_device_status.argtypes = [ctypes.POINTER(i)]
+    l.b200_sgemm_host.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz]
     l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
@@ -175,6 +176,12 @@ def gemm_splitk_static(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K:
     fit.  Calls on one device share the array: do not let two of them overlap on the GPU."""
     _check(lib().b200_sgemm_splitk_static(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M,
                                           N, K, split_k, _stream(stream)))
+
+
+def gemm_host(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int) -> None:
+    """C = A @ B for HOST matrices (raw addresses or tensors; page-locked for full speed): uploads, multiplies and
+    downloads in one pipelined, blocking call (b200_sgemm_host)."""
+    _check(lib().b200_sgemm_host(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K))
 
 
 def workspace_bytes(layout_c, layout_a, layout_b, M, N, K, variant: int = -1, split_k: int = 0) -> int:

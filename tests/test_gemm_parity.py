@@ -325,3 +325,25 @@ def test_fma_probe_runs(sgemm):
 def test_device_status_clean(sgemm):
     """No kernel launched by this module gave up a bounded wait."""
     assert sgemm.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------
+# host-buffer entry: upload, GEMM and download pipelined in one call
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("layout", LAYOUTS, ids=lambda l: layout_name(*l))
+def test_host_buffer_entry(sgemm, orc, layout):
+    la, lb, lc = layout
+    for (M, N, K) in [(2304, 320, 96), (130, 70, 33), (1024, 128, 64)]:  # several panels / one ragged panel
+        A, B = orc.fill_ab(15, la, lb, M, N, K)
+        hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+        hC = torch.full((M * N,), float("nan"), dtype=torch.float32).pin_memory()
+        sgemm.gemm_host(lc, la, lb, hC, hA, hB, M, N, K)
+        p, _ = sgemm.select_config(M, N, K, lc, la, lb)
+        want = orc.sgemm_fma(lc, la, lb, A, B, M, N, K, splits=1, k_align=p.block_k, threads=orc.max_threads())
+        assert np.array_equal(bits(hC.numpy()), bits(want)), (layout, (M, N, K))
+    # pageable host memory works too (without the overlap)
+    M, N, K = 300, 200, 64
+    A, B = orc.fill_ab(16, la, lb, M, N, K)
+    C = np.empty(M * N, dtype=np.float32)
+    sgemm.gemm_host(lc, la, lb, C.ctypes.data, A.ctypes.data, B.ctypes.data, M, N, K)
+    assert np.array_equal(bits(C), bits(orc.sgemm_fma(lc, la, lb, A, B, M, N, K)))
