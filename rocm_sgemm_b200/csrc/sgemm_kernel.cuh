@@ -603,7 +603,8 @@ __global__ void __launch_bounds__(Cfg::BLOCK_SIZE, Cfg::MIN_BLOCKS) sgemm_kernel
             if constexpr(TM == 8)
             {
                 const float4 v0 = *reinterpret_cast<const float4*>(src);
-                const float4 v1 = *reinterpret_cast<const float4*>(src + 4);
+                // second 16-byte chunk: the swizzle applies to its own index
+                const float4 v1 = *reinterpret_cast<const float4*>(as + kk * BM + ((tm0 + im * Cfg::SUB_M + 4) ^ xa));
                 float*       d  = &a_frag[buf][im * TM];
                 d[0] = v0.x; d[1] = v0.y; d[2] = v0.z; d[3] = v0.w;
                 d[4] = v1.x; d[5] = v1.y; d[6] = v1.z; d[7] = v1.w;
@@ -632,7 +633,7 @@ __global__ void __launch_bounds__(Cfg::BLOCK_SIZE, Cfg::MIN_BLOCKS) sgemm_kernel
             if constexpr(TN == 8)
             {
                 const float4 v0 = *reinterpret_cast<const float4*>(src);
-                const float4 v1 = *reinterpret_cast<const float4*>(src + 4);
+                const float4 v1 = *reinterpret_cast<const float4*>(bs + kk * BN + ((tn0 + in * Cfg::SUB_N + 4) ^ xb));
                 float*       d  = &b_frag[buf][in * TN];
                 d[0] = v0.x; d[1] = v0.y; d[2] = v0.z; d[3] = v0.w;
                 d[4] = v1.x; d[5] = v1.y; d[6] = v1.z; d[7] = v1.w;

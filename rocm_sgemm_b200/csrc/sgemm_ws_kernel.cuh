@@ -275,11 +275,11 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
 #pragma unroll
         for(int im = 0; im < Cfg::WM_CNT; ++im)
         {
-            const float* src = as + kk * BM + ((tm0 + im * Cfg::SUB_M) ^ xa);
 #pragma unroll
             for(int v = 0; v < TM / 4; ++v)
             {
-                const float4 q = *reinterpret_cast<const float4*>(src + 4 * v);
+                // the swizzle permutes 16-byte chunks: it applies to each chunk's own index
+                const float4 q = *reinterpret_cast<const float4*>(as + kk * BM + ((tm0 + im * Cfg::SUB_M + 4 * v) ^ xa));
                 float*       d = &a_frag[buf][im * TM + 4 * v];
                 d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
             }
@@ -287,11 +287,10 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
 #pragma unroll
         for(int in = 0; in < Cfg::WN_CNT; ++in)
         {
-            const float* src = bs + kk * BN + ((tn0 + in * Cfg::SUB_N) ^ xb);
 #pragma unroll
             for(int v = 0; v < TN / 4; ++v)
             {
-                const float4 q = *reinterpret_cast<const float4*>(src + 4 * v);
+                const float4 q = *reinterpret_cast<const float4*>(bs + kk * BN + ((tn0 + in * Cfg::SUB_N + 4 * v) ^ xb));
                 float*       d = &b_frag[buf][in * TN + 4 * v];
                 d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
             }
