@@ -369,7 +369,10 @@ def ours(args, w):
                                "(clocks.max.sm); MEASURED_PEAKS.json has no FP32 non-tensor entry",
                 "peak_measured_fma_probe": probe, "frac_of_measured_probe": achieved / probe,
                 "achieved_at_min_time": flops_rank / (min_ms * 1e-3) / 1e12,
-                "traffic": None, "algorithmic_flops_per_launch": flops_rank,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one sgemm_ws_kernel launch from the ncu capture
+                # summarised in profiles/sgemm_ws_kernel_4096cube_rrr.md (only this workload was captured)
+                "traffic": 390.9e6 if w["name"] == "c2" else None, "traffic_unit": "bytes per launch",
+                "algorithmic_flops_per_launch": flops_rank,
                 "algorithmic_bytes_per_launch": 4.0 * (M * K + K * Nl + M * Nl),
                 "achieved_hbm_gbs": 4.0 * (M * K + K * Nl + M * Nl) / (avg_ms * 1e-3) / 1e9}
 

@@ -150,6 +150,15 @@ def build_harness(verbose=False):
         if r.returncode != 0:
             raise RuntimeError(f"link failed for {name}:\n{r.stderr[-4000:]}")
         outs.append(exe)
+    # stand-alone probe of the packed-FMA inner loop (no library needed)
+    psrc = hdir / "inner_loop_probe.cu"
+    if psrc.exists():
+        obj = _compile(psrc, [], NVCC_FLAGS, verbose)
+        exe = BIN / "inner_loop_probe"
+        r = subprocess.run([nvcc()] + ARCH_FLAGS + ["-o", str(exe), str(obj)], capture_output=True, text=True, env=_env())
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed for inner_loop_probe:\n{r.stderr[-4000:]}")
+        outs.append(exe)
     # the tuner's one-trial executable (loads a candidate build of the library with dlopen)
     tsrc = PKG / "config" / "tuner.cpp"
     if tsrc.exists():
