@@ -347,3 +347,27 @@ def test_host_buffer_entry(sgemm, orc, layout):
     C = np.empty(M * N, dtype=np.float32)
     sgemm.gemm_host(lc, la, lb, C.ctypes.data, A.ctypes.data, B.ctypes.data, M, N, K)
     assert np.array_equal(bits(C), bits(orc.sgemm_fma(lc, la, lb, A, B, M, N, K)))
+
+
+@pytest.mark.parametrize("layout", LAYOUTS, ids=lambda l: layout_name(*l))
+def test_host_buffer_entry_strips(sgemm, orc, layout):
+    """Large problems are computed as rectangular strips (A row panels x B column panels, split-K per
+    strip).  Identity B gives C == A bit for bit under any split; random inputs meet the float64 bound."""
+    la, lb, lc = layout
+    M, N, K = 2304, 1280, 1280  # 4 x 2 pieces of 640, the last row panel shorter
+    A, _ = orc.fill_ab(17, la, lb, M, N, K, with_b=False)
+    I = orc.fill_identity(lb, K, N)
+    hA, hI = torch.from_numpy(A).pin_memory(), torch.from_numpy(I).pin_memory()
+    hC = torch.full((M * N,), float("nan"), dtype=torch.float32).pin_memory()
+    sgemm.gemm_host(lc, la, lb, hC, hA, hI, M, N, K)
+    assert np.array_equal(bits(np.ascontiguousarray(as2d(hC.numpy(), lc, M, N))),
+                          bits(np.ascontiguousarray(as2d(A, la, M, K))))
+    M, N, K = 1100, 1536, 1024  # ragged M
+    A, B = orc.fill_ab(18, la, lb, M, N, K)
+    hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+    hC = torch.full((M * N,), float("nan"), dtype=torch.float32).pin_memory()
+    sgemm.gemm_host(lc, la, lb, hC, hA, hB, M, N, K)
+    full_check_f64_on_device(la, lb, lc, A, B, M, N, K, hC.numpy(), 1e-5 * math.sqrt(K))
+    # every strip is an ordered split-K sum of FMA chains: the plain chain is within a few ulp of it
+    want = orc.sgemm_fma(lc, la, lb, A, B, M, N, K, threads=orc.max_threads())
+    assert np.max(np.abs(hC.numpy() - want)) <= 1e-4
