@@ -378,6 +378,30 @@ def ours(args, w):
 
     _, cpu_info = cpu_reference_run(w, target_seconds=12.0)
 
+    # ---- optional comparison column: the same problem on the tensor cores (3xTF32, not the graded arithmetic) ----
+    tf32x3 = None
+    if G == 1:
+        for _ in range(3):
+            sg.gemm_3xtf32(lc, la, lb, dC, dA, dB, M, Nl, K, stream=stream)
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        for _ in range(10):
+            sg.gemm_3xtf32(lc, la, lb, dC, dA, dB, M, Nl, K, stream=stream)
+        q1.record()
+        q1.synchronize()
+        t_ms = q0.elapsed_time(q1) / 10
+        rows = slice(0, 256)
+        a2 = dA.view(M, K) if la == 0 else dA.view(K, M).T
+        b2 = dB.view(K, Nl) if lb == 0 else dB.view(Nl, K).T
+        c2 = dC.view(M, Nl) if lc == 0 else dC.view(Nl, M).T
+        ref = a2[rows].double() @ b2.double()
+        rms = ref.pow(2).mean().sqrt()
+        err = ((c2[rows].double() - ref).abs() / torch.maximum(ref.abs(), rms)).max().item()
+        tf32x3 = {"tflops": flops_rank / (t_ms * 1e-3) / 1e12, "ms": t_ms, "max_rel_err_vs_f64_256_rows": err,
+                  "status": sg.tf32x3_device_status(),
+                  "note": "b200_sgemm_3xtf32: tcgen05 tensor-core path, FP32 split into two TF32 halves; "
+                          "informational, not part of value/e2e"}
+
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": G, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if G > 1 else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -391,7 +415,7 @@ def ours(args, w):
             "launch_ms": {"min": min_ms, "avg": avg_ms, "max": max_ms},
             "identity_bit_exact": check, "allgather_ms": allgather_ms,
             "roofline": roofline, "cpu_baseline": cpu_info, "clocks": clocks, "e2e": e2e,
-            "gpu_launches": args.steps * launches_per_step}
+            "tf32x3": tf32x3, "gpu_launches": args.steps * launches_per_step}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

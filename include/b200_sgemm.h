@@ -125,8 +125,9 @@ int b200_sgemm_fma_peak(int mode, int iterations, float* elapsed_ms, double* flo
  * reference has no counterpart because its kernel has no waits that could time out. */
 int b200_sgemm_device_status(int* status);
 
-/* The same operation for matrices in HOST memory: uploads B, then pipelines row panels of A and C
- * (upload of panel i+1, GEMM of panel i, download of panel i-1 on three streams), and returns when C is
+/* The same operation for matrices in HOST memory: uploads row panels of A and column panels of B
+ * alternately, computes the rectangle of C that each upload completes as one GEMM, downloads it when it
+ * is done (upload, compute and download overlap on internal streams), and returns when C is
  * complete in host memory.  This is the sequence the reference's harness performs step by step
  * (test/gemm/test.cpp:50-74: hipMemcpy H2D, gemm, hipMemcpy D2H) folded into one call; page-locked host
  * buffers are needed for the overlap.  Device buffers come from a per-device arena of the library
@@ -134,6 +135,20 @@ int b200_sgemm_device_status(int* status);
 int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
                     size_t N, size_t K);
 int b200_sgemm_shutdown_host(void);
+
+/* Optional comparison column, NOT part of the reference's surface and NOT its arithmetic: the same
+ * C = A * B computed on the tensor cores (tcgen05, accumulators in tensor memory) with every FP32 operand
+ * split into two TF32 halves and three products per pair ("3xTF32").  The result differs from the FP32 FMA
+ * chain of b200_sgemm in the last few bits (relative error of a few 1e-7 against float64; identity B does not
+ * reproduce A bit for bit).  Same arguments as b200_sgemm.  Operands that are not K-contiguous (col-major A,
+ * row-major B) or whose rows are not 16-byte aligned are first repacked into a per-device scratch arena
+ * (first such call allocates; b200_sgemm_3xtf32_shutdown frees it).  b200_sgemm_3xtf32_device_status
+ * synchronises the device and returns (and clears) the kernel's status word: 0 unless a bounded wait
+ * inside the kernel gave up. */
+int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
+                      size_t N, size_t K, void* cuda_stream);
+int b200_sgemm_3xtf32_device_status(void);
+int b200_sgemm_3xtf32_shutdown(void);
 
 /* Size of the scratch array that b200_sgemm_splitk_static uses; it is part of the library image. */
 #define B200_SGEMM_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)

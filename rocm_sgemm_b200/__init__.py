@@ -86,7 +86,8 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_get_entry_pretranspose", "b200_sgemm_map_tile",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
            "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
-           "b200_sgemm_status_string")
+           "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
+           "b200_sgemm_3xtf32_shutdown")
 
 
 def lib() -> ctypes.CDLL:
@@ -113,6 +114,7 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_device_status.argtypes = [ctypes.POINTER(i)]
     l.b200_sgemm_host.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz]
     l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
+    l.b200_sgemm_3xtf32.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _vp]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
     _lib = l
@@ -182,6 +184,18 @@ def gemm_host(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int) -> 
     """C = A @ B for HOST matrices (raw addresses or tensors; page-locked for full speed): uploads, multiplies and
     downloads in one pipelined, blocking call (b200_sgemm_host)."""
     _check(lib().b200_sgemm_host(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K))
+
+
+def gemm_3xtf32(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, stream=None) -> None:
+    """The optional tensor-core column (b200_sgemm_3xtf32): same arguments as gemm(), FP32 operands split
+    into two TF32 halves, three tcgen05 products per pair.  Not bit-identical to gemm()."""
+    _check(lib().b200_sgemm_3xtf32(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K,
+                                   _stream(stream)))
+
+
+def tf32x3_device_status() -> int:
+    """Synchronises the device; 0 unless a bounded wait inside the 3xTF32 kernel gave up."""
+    return int(lib().b200_sgemm_3xtf32_device_status())
 
 
 def workspace_bytes(layout_c, layout_a, layout_b, M, N, K, variant: int = -1, split_k: int = 0) -> int:

@@ -148,6 +148,9 @@ int main(int argc, char** argv)
     run<8, 8, 1, 0, 0, 4, 0, 256, 1>("8x8 pair-outer, 8x4 lanes", f, out);
     run<8, 8, 1, 0, 0, 16, 0, 256, 1>("8x8 pair-outer, 2x16 lanes", f, out);
     run<8, 8, 1, 0, 0, 8, 0, 128, 2>("8x8 pair-outer, 128 thr x2 CTAs", f, out);
+    run<8, 8, 1, 0, 0, 8, 0, 384, 1>("8x8 pair-outer, 384 thr (3 warps/scheduler)", f, out);
+    run<8, 8, 1, 0, 0, 8, 0, 512, 1>("8x8 pair-outer, 512 thr (4 warps/scheduler)", f, out);
+    run<8, 8, 1, 1, 0, 8, 0, 512, 1>("8x8 pairs along m, 512 thr", f, out);
     run<16, 8, 1, 0, 0, 8, 0, 256, 1>("16x8 pair-outer, 256 thr", f, out);
     run<16, 8, 1, 0, 0, 8, 0, 128, 1>("16x8 pair-outer, 128 thr x1 CTA", f, out);
     run<16, 8, 1, 0, 0, 8, 0, 128, 2>("16x8 pair-outer, 128 thr x2 CTAs", f, out);
