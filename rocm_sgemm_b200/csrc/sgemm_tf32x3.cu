@@ -2,19 +2,26 @@
 // halves (the "3xTF32" scheme).  A separate, optional entry beside the true-FP32 FMA path: it is NOT
 // bit-identical to the reference's arithmetic (rocm_sgemm/include/rocm_sgemm/kernel/kernel.hpp:188-266
 // is an FP32 FMA chain) and has no counterpart in the reference; it exists as a comparison column
-// showing what the same FP32 problem costs when an error of a few 1e-7 relative is acceptable.
+// showing what the same FP32 problem costs when a relative error of about 2e-6 is acceptable.
 //
 //   a = a_hi + a_lo,  a_hi = tf32(a),  a_lo = tf32(a - a_hi)          (both round-to-nearest)
-//   A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi                          (FP32 accumulation in tensor memory)
+//   A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi                          (three tensor-core products)
 //
-// Kernel (one persistent CTA per SM, 128 x BN tiles, K blocks of 32 floats = one 128-byte swizzle row):
-//   warp 8      TMA producer: cp.async.bulk.tensor.2d of the raw FP32 A and B tiles (K-major, 128B swizzle)
-//   warps 4-7   converters: rewrite each tile in place as its hi half and write the lo half next to it
-//               (elementwise, so the swizzled placement is preserved), then fence to the async proxy
-//   warp 9      one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), 12 per K block, accumulating
-//               into one of two TMEM accumulators; tcgen05.commit releases the stage / publishes the tile
-//   warps 0-3   epilogue: tcgen05.ld the finished accumulator (warp w owns TMEM lanes 32w..32w+31 = tile
-//               rows) and store C, while the MMA warp already works on the next tile in the other buffer
+// Kernel: one persistent CTA per SM, 128 x 128 tiles, K blocks of 32 floats (= one 128-byte swizzle row).
+//   warp 16     TMA producer: cp.async.bulk.tensor.2d of the raw FP32 A and B tiles (K-major, 128B swizzle)
+//               into a ring of raw stages
+//   warps 8-15  converters: read a raw stage, write the hi and lo halves of both tiles into a ring of
+//               converted stages (elementwise and position preserving, so the swizzled placement stays
+//               valid), fence to the async proxy, release the raw stage
+//   warp 17     one thread issues tcgen05.mma.kind::tf32 (M=128, N=128, K=8), 12 per K block, into one of
+//               two accumulators in tensor memory; tcgen05.commit releases the converted stage and, every
+//               T_CHUNK K blocks, publishes the partial sum
+//   warps 0-7   accumulate + epilogue: tcgen05.ld the finished partial sum (warp w owns TMEM lanes
+//               32*(w%4).. = tile rows, and columns 64*(w/4)..), add it to register accumulators, store C
+//               at the end of the tile.  The tensor core adds into its FP32 accumulator with truncation,
+//               which biases long sums (measured: error growing linearly with K, 2.4e-5 at K = 1024); moving
+//               the sum to registers (round-to-nearest adds) every 64 k keeps the error at about 1.7e-6
+//               for every K.
 // Operands must be K-contiguous for this kernel (A row-major, B col-major); the host entry repacks the
 // other layouts (and operands whose pitch is not a multiple of 16 bytes) into a scratch arena first.
 // Every mbarrier wait is bounded; on a time-out the CTA records a status word, stops and frees its TMEM.
@@ -31,23 +38,32 @@ namespace
 {
 using namespace sgemm_b200;
 
-constexpr int T_BM      = 128;
-constexpr int T_BK      = 32; // floats: 128 bytes, one swizzle row
-constexpr int T_THREADS = 320;
-constexpr int T_CHUNK   = 2;  // K blocks accumulated inside the tensor core before the sum moves to registers
-constexpr int T_ERR_WAIT = 16; // status bit: some wait in the tensor-core kernel timed out
+constexpr int T_BM           = 128;
+constexpr int T_BK           = 32;  // floats: 128 bytes, one swizzle row
+constexpr int T_ACCUMULATORS = 256; // warps 0-7
+constexpr int T_CONVERTERS   = 256; // warps 8-15
+constexpr int T_TMA_WARP     = 16;
+constexpr int T_MMA_WARP     = 17;
+constexpr int T_THREADS      = 576;
+constexpr int T_CHUNK        = 2;  // K blocks accumulated inside the tensor core before the sum moves to registers
+constexpr int T_ERR_WAIT     = 16; // status bit: a wait in this kernel timed out; bits 8..13 say which one first
 
 __device__ int g_tf32_status;
 
 template<int BN>
 struct TLayout
 {
-    static constexpr int    A_BYTES     = T_BM * T_BK * 4; // 16 KB
-    static constexpr int    B_BYTES     = BN * T_BK * 4;
-    static constexpr int    STAGE_BYTES = 2 * (A_BYTES + B_BYTES); // hi + lo of both
-    static constexpr int    STAGES      = (200 * 1024) / STAGE_BYTES;
-    static constexpr size_t SMEM_BYTES  = size_t(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static constexpr int    TMEM_COLS   = 2 * BN; // two accumulators
+    static constexpr int    A_BYTES    = T_BM * T_BK * 4; // 16 KB
+    static constexpr int    B_BYTES    = BN * T_BK * 4;
+    static constexpr int    RAW_BYTES  = A_BYTES + B_BYTES;       // what TMA delivers per K block
+    static constexpr int    CVT_BYTES  = 2 * (A_BYTES + B_BYTES); // hi + lo halves of both tiles
+    static constexpr int    CVT_STAGES = 2;
+    static constexpr int    RAW_STAGES = (224 * 1024 - CVT_STAGES * CVT_BYTES) / RAW_BYTES;
+    static constexpr int    BARRIERS   = 2 * RAW_STAGES + 2 * CVT_STAGES + 4;
+    static constexpr size_t SMEM_BYTES = size_t(RAW_STAGES) * RAW_BYTES + size_t(CVT_STAGES) * CVT_BYTES
+                                         + 1024 /*alignment slack*/ + 256 /*barriers, TMEM address, abort flag*/;
+    static constexpr int    TMEM_COLS  = 2 * BN; // two partial accumulators
+    static_assert(8 * BARRIERS + 16 <= 256, "barrier area");
 };
 
 struct TArgs
@@ -116,11 +132,23 @@ __device__ __forceinline__ constexpr uint32_t umma_idesc_tf32()
 {
     return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(BN >> 3) << 17) | (uint32_t(T_BM >> 4) << 24);
 }
+// Round-to-nearest TF32 (10 mantissa bits) with integer instructions: measured 9 % faster for the whole
+// kernel than cvt.rna.tf32.f32, whose issue rate is lower; the results are identical except on ties.
 __device__ __forceinline__ float to_tf32(float x)
 {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+}
+
+// Tile order: bands of 16 tile rows, tile columns advancing inside a band, so that the CTAs running at the same
+// time share 16 row panels of A and about nine column panels of B (about 100 MB at K = 8192: within the L2).
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn)
+{
+    constexpr int BAND = 16;
+    const int     band = tile / (BAND * tiles_n);
+    const int     rows = min(BAND, tiles_m - band * BAND);
+    const int     idx  = tile - band * BAND * tiles_n;
+    tm = band * BAND + idx % rows;
+    tn = idx / rows;
 }
 
 template<int BN>
@@ -129,40 +157,46 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                         const __grid_constant__ CUtensorMap map_b)
 {
     using L = TLayout<BN>;
-    constexpr int STAGES = L::STAGES;
+    constexpr int RAW = L::RAW_STAGES, CVT = L::CVT_STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr  = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t tile_base = (raw_addr + 1023u) & ~1023u;
     uint8_t*       tiles     = smem_raw + (tile_base - raw_addr);
-    const uint32_t bar_base  = tile_base + STAGES * L::STAGE_BYTES;
-    // barriers: raw_full[S], cvt_full[S], empty[S], acc_full[2], acc_empty[2]; then the TMEM address and the abort flag
+    // [RAW raw stages: A, B as TMA wrote them][CVT converted stages: A_hi, A_lo, B_hi, B_lo][barriers]
+    const uint32_t cvt_base = tile_base + RAW * L::RAW_BYTES;
+    const uint32_t bar_base = cvt_base + CVT * L::CVT_BYTES;
     auto raw_full  = [&](int s) { return bar_base + 8u * s; };
-    auto cvt_full  = [&](int s) { return bar_base + 8u * (STAGES + s); };
-    auto empty     = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
-    auto acc_full  = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };
-    auto acc_empty = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 + b); };
-    uint8_t*      misc       = tiles + STAGES * L::STAGE_BYTES + 8 * (3 * STAGES + 4);
+    auto raw_empty = [&](int s) { return bar_base + 8u * (RAW + s); };
+    auto cvt_full  = [&](int s) { return bar_base + 8u * (2 * RAW + s); };
+    auto cvt_empty = [&](int s) { return bar_base + 8u * (2 * RAW + CVT + s); };
+    auto acc_full  = [&](int b) { return bar_base + 8u * (2 * RAW + 2 * CVT + b); };
+    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * RAW + 2 * CVT + 2 + b); };
+    uint8_t*      misc       = tiles + RAW * L::RAW_BYTES + CVT * L::CVT_BYTES + 8 * (2 * RAW + 2 * CVT + 4);
     uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if(threadIdx.x == 0)
     {
-        for(int s = 0; s < STAGES; ++s)
+        for(int s = 0; s < RAW; ++s)
         {
             mbar_init(raw_full(s), 1);
-            mbar_init(cvt_full(s), 128);
-            mbar_init(empty(s), 1);
+            mbar_init(raw_empty(s), T_CONVERTERS);
+        }
+        for(int s = 0; s < CVT; ++s)
+        {
+            mbar_init(cvt_full(s), T_CONVERTERS);
+            mbar_init(cvt_empty(s), 1);
         }
         for(int b = 0; b < 2; ++b)
         {
             mbar_init(acc_full(b), 1);
-            mbar_init(acc_empty(b), 128);
+            mbar_init(acc_empty(b), T_ACCUMULATORS);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if(warp == 9)
+    if(warp == T_MMA_WARP)
     {
         tmem_alloc((uint32_t)__cvta_generic_to_shared(tmem_slot), L::TMEM_COLS);
         tmem_relinquish();
@@ -174,12 +208,13 @@ __global__ void __launch_bounds__(T_THREADS, 1)
 
     const int total_tiles = t.tiles_m * t.tiles_n;
     const int kblocks     = (t.K + T_BK - 1) / T_BK;
-    auto fail = [&]() {
-        *abort_flag = 1;
-        atomicOr(t.status, T_ERR_WAIT);
+    // the first wait of the CTA that gives up records where (bits 8..13) and raises the abort flag for the others
+    auto fail = [&](int where) {
+        if(atomicExch(const_cast<int*>(abort_flag), 1) == 0)
+            atomicOr(t.status, T_ERR_WAIT | (256 << where));
     };
 
-    if(warp == 8)
+    if(warp == T_TMA_WARP)
     {
         // ---------------- TMA producer ----------------
         if(lane == 0)
@@ -188,58 +223,77 @@ __global__ void __launch_bounds__(T_THREADS, 1)
             bool     ok = true;
             for(int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
             {
-                const int tm = tile % t.tiles_m, tn = tile / t.tiles_m;
+                int tm, tn;
+                tile_coords(tile, t.tiles_m, t.tiles_n, tm, tn);
                 for(int kb = 0; kb < kblocks; ++kb, ++it)
                 {
-                    const int      s  = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if(!mbar_wait(empty(s), ph ^ 1, abort_flag)) { fail(); ok = false; break; }
-                    const uint32_t st = tile_base + s * L::STAGE_BYTES;
-                    mbar_arrive_expect_tx(raw_full(s), L::A_BYTES + L::B_BYTES);
+                    const int      s  = it % RAW;
+                    const uint32_t ph = (it / RAW) & 1;
+                    if(!mbar_wait(raw_empty(s), ph ^ 1, abort_flag)) { fail(0); ok = false; break; }
+                    const uint32_t st = tile_base + s * L::RAW_BYTES;
+                    mbar_arrive_expect_tx(raw_full(s), L::RAW_BYTES);
                     tma_load_2d(st, &map_a, kb * T_BK, tm * T_BM, raw_full(s));
-                    tma_load_2d(st + 2 * L::A_BYTES, &map_b, kb * T_BK, tn * BN, raw_full(s));
+                    tma_load_2d(st + L::A_BYTES, &map_b, kb * T_BK, tn * BN, raw_full(s));
                 }
             }
         }
     }
-    else if(warp >= 4 && warp < 8)
+    else if(warp >= T_ACCUMULATORS / 32 && warp < T_TMA_WARP)
     {
-        // ---------------- converters: raw FP32 -> hi (in place) and lo ----------------
-        const int ct = threadIdx.x - 128;
+        // ---------------- converters: raw FP32 -> hi and lo TF32 halves ----------------
+        // Elementwise and position preserving, so the 128-byte swizzle TMA applied stays valid for both halves.
+        const int ct = threadIdx.x - T_ACCUMULATORS;
         uint32_t  it = 0;
         bool      ok = true;
         for(int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
         {
             for(int kb = 0; kb < kblocks; ++kb, ++it)
             {
-                const int      s  = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                if(!mbar_wait(raw_full(s), ph, abort_flag)) { fail(); ok = false; break; }
-                uint8_t* st = tiles + s * L::STAGE_BYTES;
-                float4*  a_hi = reinterpret_cast<float4*>(st);
-                float4*  a_lo = reinterpret_cast<float4*>(st + L::A_BYTES);
-                float4*  b_hi = reinterpret_cast<float4*>(st + 2 * L::A_BYTES);
-                float4*  b_lo = reinterpret_cast<float4*>(st + 2 * L::A_BYTES + L::B_BYTES);
-                auto split = [](float4* hi, float4* lo, int i) {
-                    const float4 v = hi[i];
-                    float4       h, l;
-                    h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
-                    l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y); l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
-                    hi[i] = h;
-                    lo[i] = l;
+                const int      rs = it % RAW, cs = it % CVT;
+                const uint32_t rph = (it / RAW) & 1, cph = (it / CVT) & 1;
+                if(!mbar_wait(raw_full(rs), rph, abort_flag)) { fail(1); ok = false; break; }
+                if(!mbar_wait(cvt_empty(cs), cph ^ 1, abort_flag)) { fail(2); ok = false; break; }
+                const float4* raw = reinterpret_cast<const float4*>(tiles + rs * L::RAW_BYTES);
+                uint8_t*      cv  = tiles + RAW * L::RAW_BYTES + cs * L::CVT_BYTES;
+                float4*       a_hi = reinterpret_cast<float4*>(cv);
+                float4*       a_lo = reinterpret_cast<float4*>(cv + L::A_BYTES);
+                float4*       b_hi = reinterpret_cast<float4*>(cv + 2 * L::A_BYTES);
+                float4*       b_lo = reinterpret_cast<float4*>(cv + 2 * L::A_BYTES + L::B_BYTES);
+                constexpr int NA = L::A_BYTES / 16 / T_CONVERTERS, NB = L::B_BYTES / 16 / T_CONVERTERS;
+                float4        v[NA + NB];
+#pragma unroll
+                for(int i = 0; i < NA; ++i)
+                    v[i] = raw[ct + T_CONVERTERS * i];
+#pragma unroll
+                for(int i = 0; i < NB; ++i)
+                    v[NA + i] = raw[L::A_BYTES / 16 + ct + T_CONVERTERS * i];
+                auto split = [](const float4& x, float4& h, float4& l) {
+                    h.x = to_tf32(x.x); h.y = to_tf32(x.y); h.z = to_tf32(x.z); h.w = to_tf32(x.w);
+                    l.x = to_tf32(x.x - h.x); l.y = to_tf32(x.y - h.y); l.z = to_tf32(x.z - h.z); l.w = to_tf32(x.w - h.w);
                 };
 #pragma unroll
-                for(int i = 0; i < L::A_BYTES / 16 / 128; ++i)
-                    split(a_hi, a_lo, ct + 128 * i);
+                for(int i = 0; i < NA; ++i)
+                {
+                    float4 h, l;
+                    split(v[i], h, l);
+                    a_hi[ct + T_CONVERTERS * i] = h;
+                    a_lo[ct + T_CONVERTERS * i] = l;
+                }
 #pragma unroll
-                for(int i = 0; i < L::B_BYTES / 16 / 128; ++i)
-                    split(b_hi, b_lo, ct + 128 * i);
-                fence_async_smem();
-                mbar_arrive(cvt_full(s));
+                for(int i = 0; i < NB; ++i)
+                {
+                    float4 h, l;
+                    split(v[NA + i], h, l);
+                    b_hi[ct + T_CONVERTERS * i] = h;
+                    b_lo[ct + T_CONVERTERS * i] = l;
+                }
+                mbar_arrive(raw_empty(rs)); // the raw stage has been read: TMA may refill it
+                fence_async_smem();         // the converted tiles are read by the tensor core (async proxy)
+                mbar_arrive(cvt_full(cs));
             }
         }
     }
-    else if(warp == 9)
+    else if(warp == T_MMA_WARP)
     {
         // ---------------- MMA issuer ----------------
         if(lane == 0)
@@ -251,20 +305,20 @@ __global__ void __launch_bounds__(T_THREADS, 1)
             {
                 for(int kb = 0; kb < kblocks; ++kb, ++it)
                 {
-                    // a new partial accumulator every T_CHUNK K blocks (drained into registers by the epilogue warps)
+                    // a new partial accumulator every T_CHUNK K blocks (drained into registers by the accumulate warps)
                     const bool     first = kb % T_CHUNK == 0;
                     const uint32_t buf = ccount & 1, aph = (ccount >> 1) & 1;
                     if(first)
                     {
-                        if(!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag)) { fail(); ok = false; break; }
+                        if(!mbar_wait(acc_empty(buf), aph ^ 1, abort_flag)) { fail(3); ok = false; break; }
                         tc_fence_after();
                     }
                     const uint32_t d  = tmem_base + buf * BN;
-                    const int      s  = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if(!mbar_wait(cvt_full(s), ph, abort_flag)) { fail(); ok = false; break; }
+                    const int      s  = it % CVT;
+                    const uint32_t ph = (it / CVT) & 1;
+                    if(!mbar_wait(cvt_full(s), ph, abort_flag)) { fail(4); ok = false; break; }
                     tc_fence_after();
-                    const uint32_t st   = tile_base + s * L::STAGE_BYTES;
+                    const uint32_t st   = cvt_base + s * L::CVT_BYTES;
                     const uint32_t a_hi = st, a_lo = st + L::A_BYTES, b_hi = st + 2 * L::A_BYTES,
                                    b_lo = st + 2 * L::A_BYTES + L::B_BYTES;
 #pragma unroll
@@ -277,7 +331,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                         tc_mma_tf32(d, dah, dbl, idesc, 1);
                         tc_mma_tf32(d, dah, dbh, idesc, 1);
                     }
-                    tc_commit(empty(s)); // the stage may be refilled once these MMAs have read it
+                    tc_commit(cvt_empty(s)); // the converted stage may be rewritten once these MMAs have read it
                     if(kb % T_CHUNK == T_CHUNK - 1 || kb == kblocks - 1)
                     {
                         tc_commit(acc_full(buf)); // the partial sum is complete once every MMA above has finished
@@ -289,27 +343,31 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     }
     else
     {
-        // ---------------- accumulate + epilogue warps 0-3 ----------------
-        // Thread = one row of the tile.  The tensor core adds into its FP32 accumulator with truncation, which
-        // biases long sums; so the MMA warp starts a fresh TMEM accumulator every T_CHUNK K blocks and these
-        // warps add the finished partial sums in registers with round-to-nearest.
-        uint32_t ccount = 0;
-        bool     ok     = true;
-        const int chunks = (kblocks + T_CHUNK - 1) / T_CHUNK;
+        // ---------------- accumulate + epilogue warps ----------------
+        // Thread = one row of the tile and one half of its columns (warp w: TMEM lanes 32*(w%4).., columns
+        // (w/4)*BN/2..).  The tensor core adds into its FP32 accumulator with truncation, which biases long
+        // sums; so the MMA warp starts a fresh TMEM accumulator every T_CHUNK K blocks and these warps add
+        // the finished partial sums in registers with round-to-nearest.
+        constexpr int HALF = BN / 2;
+        const int     q = warp & 3, h = warp >> 2;
+        uint32_t      ccount = 0;
+        bool          ok     = true;
+        const int     chunks = (kblocks + T_CHUNK - 1) / T_CHUNK;
         for(int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
         {
-            const int tm = tile % t.tiles_m, tn = tile / t.tiles_m;
-            float     acc[BN];
+            int tm, tn;
+            tile_coords(tile, t.tiles_m, t.tiles_n, tm, tn);
+            float     acc[HALF];
             for(int ch = 0; ch < chunks; ++ch, ++ccount)
             {
                 const uint32_t buf = ccount & 1, aph = (ccount >> 1) & 1;
-                if(!mbar_wait(acc_full(buf), aph, abort_flag)) { fail(); ok = false; break; }
+                if(!mbar_wait(acc_full(buf), aph, abort_flag)) { fail(5); ok = false; break; }
                 tc_fence_after();
 #pragma unroll
-                for(int c = 0; c < BN / 32; ++c)
+                for(int c = 0; c < HALF / 32; ++c)
                 {
                     uint32_t v[32];
-                    tmem_ld32(tmem_base + buf * BN + c * 32 + (uint32_t(warp * 32) << 16), v);
+                    tmem_ld32(tmem_base + buf * BN + h * HALF + c * 32 + (uint32_t(q * 32) << 16), v);
                     tmem_ld_wait();
                     if(ch == 0)
                     {
@@ -329,12 +387,12 @@ __global__ void __launch_bounds__(T_THREADS, 1)
             }
             if(!ok)
                 break;
-            const int  row    = tm * T_BM + warp * 32 + lane;
+            const int  row    = tm * T_BM + q * 32 + lane;
             const bool row_ok = row < t.M;
 #pragma unroll
-            for(int c = 0; c < BN / 32; ++c)
+            for(int c = 0; c < HALF / 32; ++c)
             {
-                const int col0 = tn * BN + c * 32;
+                const int col0 = tn * BN + h * HALF + c * 32;
                 if(t.layout_c == B200_SGEMM_ROW_MAJOR)
                 {
                     if(row_ok)
@@ -370,7 +428,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     __syncwarp();
     tc_fence_before();
     __syncthreads();
-    if(warp == 9)
+    if(warp == T_MMA_WARP)
     {
         tc_fence_after();
         tmem_dealloc(tmem_base, L::TMEM_COLS);
@@ -557,6 +615,7 @@ extern "C" int b200_sgemm_3xtf32_device_status(void)
         cudaMemcpyToSymbol(g_tf32_status, &zero, sizeof(int));
     return v;
 }
+
 
 extern "C" int b200_sgemm_3xtf32_shutdown(void)
 {
