@@ -136,6 +136,26 @@ int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* C, const fl
                     size_t N, size_t K);
 int b200_sgemm_shutdown_host(void);
 
+/* The same product for `batch` matrices at fixed element strides: matrix b uses C + b*stride_c, A + b*stride_a,
+ * B + b*stride_b (stride_a or stride_b may be 0 to share an operand; the C matrices must not overlap).  The
+ * reference's benchmark has a --batch_count switch that only replicates buffers
+ * (benchmark/gemm/bench.cpp:49-64,213-216); this entry computes every matrix, one launch per matrix on the
+ * stream, with the drop-in entry's table lookup and arena. */
+int b200_sgemm_strided_batched(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
+                               size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a, size_t stride_b,
+                               size_t batch, void* cuda_stream);
+
+/* Vendor-BLAS calling convention on this library's kernels: column-major C (ldc >= M),
+ * C = alpha * op(A) * op(B) + beta * C, op(X) = X or X^T by trans_x (0 / 1), A stored (trans_a ? K x M : M x K)
+ * with lda, B stored (trans_b ? N x K : K x N) with ldb.  With alpha = 1 and beta = 0 this is the mapping of
+ * rocblas_wrapper::gemm<TRANSPOSE_A, TRANSPOSE_B> (rocblas_wrapper/src/gemm.cpp:45-60) and runs exactly the
+ * kernels of b200_sgemm_ex.  Otherwise the product goes to a per-(device, stream) scratch matrix and one more
+ * pass forms fl(fl(alpha*t) + fl(beta*c)) per element (three FP32 roundings, no contraction; beta = 0 does not
+ * read C).  b200_sgemm_blas_shutdown frees the scratch. */
+int b200_sgemm_blas(int trans_a, int trans_b, size_t M, size_t N, size_t K, float alpha, const float* A, size_t lda,
+                    const float* B, size_t ldb, float beta, float* C, size_t ldc, void* cuda_stream);
+int b200_sgemm_blas_shutdown(void);
+
 /* Optional comparison column, NOT part of the reference's surface and NOT its arithmetic: the same
  * C = A * B computed on the tensor cores (tcgen05, accumulators in tensor memory) with every FP32 operand
  * split into two TF32 halves and three products per pair ("3xTF32").  The result differs from the FP32 FMA

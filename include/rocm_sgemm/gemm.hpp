@@ -106,6 +106,21 @@ ROCM_SGEMM_DEFINE_GEMM(col_major, col_major, row_major)
 ROCM_SGEMM_DEFINE_GEMM(col_major, col_major, col_major)
 #undef ROCM_SGEMM_DEFINE_GEMM
 
+// The signature of the reference's vendor wrapper, rocblas_wrapper::gemm<TRANSPOSE_A, TRANSPOSE_B>(C, A, B, M, N, K,
+// stream) (rocblas_wrapper/include/rocblas_wrapper/gemm.hpp:55-68; column-major C, lda = TA ? K : M,
+// ldb = TB ? N : K, ldc = M), served by this library's own kernels instead of the vendor BLAS.
+namespace blas
+{
+template<bool TRANSPOSE_A, bool TRANSPOSE_B>
+inline void gemm(float* C, float* A, float* B, size_t M, size_t N, size_t K, cudaStream_t& stream)
+{
+    const int status = b200_sgemm_blas(TRANSPOSE_A, TRANSPOSE_B, M, N, K, 1.0f, A, TRANSPOSE_A ? K : M, B,
+                                       TRANSPOSE_B ? N : K, 0.0f, C, M, stream);
+    if(status != B200_SGEMM_OK)
+        throw std::runtime_error(std::string("rocm_sgemm::blas::gemm: ") + b200_sgemm_status_string(status));
+}
+} // namespace blas
+
 } // namespace rocm_sgemm
 
 #endif // ROCM_SGEMM_GEMM_HPP

@@ -87,7 +87,8 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
            "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
-           "b200_sgemm_3xtf32_shutdown")
+           "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
+           "b200_sgemm_blas_shutdown")
 
 
 def lib() -> ctypes.CDLL:
@@ -115,6 +116,8 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_host.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz]
     l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_3xtf32.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _vp]
+    l.b200_sgemm_strided_batched.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _vp]
+    l.b200_sgemm_blas.argtypes = [i, i, _sz, _sz, _sz, ctypes.c_float, _vp, _sz, _vp, _sz, ctypes.c_float, _vp, _sz, _vp]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
     _lib = l
@@ -184,6 +187,20 @@ def gemm_host(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int) -> 
     """C = A @ B for HOST matrices (raw addresses or tensors; page-locked for full speed): uploads, multiplies and
     downloads in one pipelined, blocking call (b200_sgemm_host)."""
     _check(lib().b200_sgemm_host(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K))
+
+
+def gemm_strided_batched(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, stride_c: int, stride_a: int,
+                         stride_b: int, batch: int, stream=None) -> None:
+    """`batch` products at fixed element strides (stride_a / stride_b may be 0 to share an operand)."""
+    _check(lib().b200_sgemm_strided_batched(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N,
+                                            K, stride_c, stride_a, stride_b, batch, _stream(stream)))
+
+
+def gemm_blas(trans_a: bool, trans_b: bool, M: int, N: int, K: int, alpha: float, A, lda: int, B, ldb: int, beta: float,
+              C, ldc: int, stream=None) -> None:
+    """Vendor-BLAS convention: column-major C = alpha * op(A) op(B) + beta * C with leading dimensions."""
+    _check(lib().b200_sgemm_blas(int(bool(trans_a)), int(bool(trans_b)), M, N, K, float(alpha), _ptr(A), lda, _ptr(B),
+                                 ldb, float(beta), _ptr(C), ldc, _stream(stream)))
 
 
 def gemm_3xtf32(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, stream=None) -> None:

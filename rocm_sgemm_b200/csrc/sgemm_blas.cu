@@ -1,0 +1,150 @@
+// API breadth beside the drop-in entry, built on the public C ABI only (b200_sgemm / b200_sgemm_ex):
+//
+//   b200_sgemm_strided_batched  the same product for `batch` matrices at fixed element strides.  The reference's
+//                               benchmark carries a --batch_count switch that replicates its buffers
+//                               (benchmark/gemm/bench.cpp:49-64,213-216) but its kernel multiplies one matrix;
+//                               here every matrix of the batch is computed, one launch per matrix on the stream.
+//   b200_sgemm_blas             the vendor-BLAS calling convention: column-major C, op(A) / op(B) selected by
+//                               transpose flags, leading dimensions, alpha and beta.  With alpha = 1, beta = 0 it is
+//                               the argument mapping of rocblas_wrapper::gemm<TRANSPOSE_A, TRANSPOSE_B>
+//                               (rocblas_wrapper/src/gemm.cpp:45-60: lda = TA ? K : M, ldb = TB ? N : K, ldc = M) onto
+//                               this library's kernels.  Other alpha / beta: the product goes to a scratch matrix
+//                               and one HBM-bound pass forms C = alpha * (A B) + beta * C with three separately
+//                               rounded FP32 operations (product, product, sum; no contraction), so that a host
+//                               restatement reproduces it bit for bit.  beta = 0 never reads C.
+#include "../../include/b200_sgemm.h"
+
+#include <cuda_runtime.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
+
+namespace
+{
+// C[j * ldc + i] = alpha * T[j * M + i] + beta * C[j * ldc + i], T packed column-major M x N
+__global__ void __launch_bounds__(256) axpby_kernel(float* __restrict__ C, const float* __restrict__ T, size_t M, size_t N,
+                                                    size_t ldc, float alpha, float beta)
+{
+    const size_t total  = M * N;
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for(size_t e = size_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride)
+    {
+        const size_t j = e / M, i = e - j * M;
+        float*       c = C + j * ldc + i;
+        const float  p = __fmul_rn(alpha, T[e]);
+        *c             = beta == 0.f ? p : __fadd_rn(p, __fmul_rn(beta, *c));
+    }
+}
+
+struct Scratch
+{
+    void*  ptr   = nullptr;
+    size_t bytes = 0;
+};
+std::mutex                                      g_mutex;
+std::map<std::pair<int, cudaStream_t>, Scratch> g_scratch;
+
+// scratch block of this (device, stream); grows on demand (synchronising the stream first, as queued work may
+// still use the old block)
+cudaError_t scratch_get(cudaStream_t stream, size_t bytes, void** out)
+{
+    int         device = 0;
+    cudaError_t e      = cudaGetDevice(&device);
+    if(e != cudaSuccess)
+        return e;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    Scratch&                    s = g_scratch[std::make_pair(device, stream)];
+    if(s.bytes < bytes)
+    {
+        if(s.ptr)
+        {
+            if((e = cudaStreamSynchronize(stream)) != cudaSuccess)
+                return e;
+            cudaFree(s.ptr);
+            s.ptr   = nullptr;
+            s.bytes = 0;
+        }
+        if((e = cudaMalloc(&s.ptr, bytes)) != cudaSuccess)
+            return e;
+        s.bytes = bytes;
+    }
+    *out = s.ptr;
+    return cudaSuccess;
+}
+} // namespace
+
+extern "C" int b200_sgemm_strided_batched(int layout_c, int layout_a, int layout_b, float* C, const float* A,
+                                          const float* B, size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a,
+                                          size_t stride_b, size_t batch, void* cuda_stream)
+{
+    if(batch == 0)
+        return B200_SGEMM_INVALID_ARGUMENT;
+    // C matrices must not overlap; A or B may be shared by the whole batch (stride 0)
+    if(batch > 1 && stride_c < M * N)
+        return B200_SGEMM_INVALID_ARGUMENT;
+    for(size_t b = 0; b < batch; ++b)
+    {
+        const int st = b200_sgemm(layout_c, layout_a, layout_b, C ? C + b * stride_c : nullptr,
+                                  A ? A + b * stride_a : nullptr, B ? B + b * stride_b : nullptr, M, N, K, cuda_stream);
+        if(st != B200_SGEMM_OK)
+            return st;
+    }
+    return B200_SGEMM_OK;
+}
+
+extern "C" int b200_sgemm_blas(int trans_a, int trans_b, size_t M, size_t N, size_t K, float alpha, const float* A,
+                               size_t lda, const float* B, size_t ldb, float beta, float* C, size_t ldc, void* cuda_stream)
+{
+    if((trans_a | trans_b) & ~1)
+        return B200_SGEMM_INVALID_ARGUMENT;
+    if(!C || !A || !B || M == 0 || N == 0 || K == 0)
+        return B200_SGEMM_INVALID_ARGUMENT;
+    // column-major storage: op(A) = A (M x K, lda >= M) is col-major; op(A) = A^T means A is stored K x M, i.e. the
+    // M x K operand is row-major with pitch lda >= K.  Likewise for B.
+    const int la = trans_a ? B200_SGEMM_ROW_MAJOR : B200_SGEMM_COL_MAJOR;
+    const int lb = trans_b ? B200_SGEMM_ROW_MAJOR : B200_SGEMM_COL_MAJOR;
+    if(lda < (trans_a ? K : M) || ldb < (trans_b ? N : K) || ldc < M)
+        return B200_SGEMM_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    const bool   plain  = alpha == 1.f && beta == 0.f;
+    // the table's split-K needs a workspace; the scratch block holds [T (only when alpha/beta apply)][workspace]
+    const size_t ws_bytes = b200_sgemm_workspace_bytes(B200_SGEMM_COL_MAJOR, la, lb, M, N, K, -1, 0);
+    const size_t t_bytes  = plain ? 0 : (M * N * sizeof(float) + 255) / 256 * 256;
+    char*        block    = nullptr;
+    if(ws_bytes + t_bytes > 0)
+    {
+        void*       p = nullptr;
+        cudaError_t e = scratch_get(stream, ws_bytes + t_bytes, &p);
+        if(e != cudaSuccess)
+            return (int)e;
+        block = static_cast<char*>(p);
+    }
+    float* T  = plain ? C : reinterpret_cast<float*>(block);
+    void*  ws = ws_bytes ? block + t_bytes : nullptr;
+    int    st = b200_sgemm_ex(B200_SGEMM_COL_MAJOR, la, lb, T, A, B, M, N, K, lda, ldb, plain ? ldc : M, -1, 0, ws, ws_bytes,
+                              cuda_stream);
+    if(st != B200_SGEMM_OK || plain)
+        return st;
+    const size_t total  = M * N;
+    size_t       blocks = (total + 255) / 256;
+    if(blocks > 148 * 16)
+        blocks = 148 * 16;
+    axpby_kernel<<<(unsigned)blocks, 256, 0, stream>>>(C, T, M, N, ldc, alpha, beta);
+    return (int)cudaPeekAtLastError();
+}
+
+extern "C" int b200_sgemm_blas_shutdown(void)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int                         saved = 0;
+    cudaGetDevice(&saved);
+    for(auto& kv : g_scratch)
+    {
+        cudaSetDevice(kv.first.first);
+        cudaFree(kv.second.ptr);
+    }
+    g_scratch.clear();
+    cudaSetDevice(saved);
+    return B200_SGEMM_OK;
+}

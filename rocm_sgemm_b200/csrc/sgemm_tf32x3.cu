@@ -181,17 +181,17 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         for(int s = 0; s < RAW; ++s)
         {
             mbar_init(raw_full(s), 1);
-            mbar_init(raw_empty(s), T_CONVERTERS);
+            mbar_init(raw_empty(s), T_CONVERTERS / 32);
         }
         for(int s = 0; s < CVT; ++s)
         {
-            mbar_init(cvt_full(s), T_CONVERTERS);
+            mbar_init(cvt_full(s), T_CONVERTERS / 32);
             mbar_init(cvt_empty(s), 1);
         }
         for(int b = 0; b < 2; ++b)
         {
             mbar_init(acc_full(b), 1);
-            mbar_init(acc_empty(b), T_ACCUMULATORS);
+            mbar_init(acc_empty(b), T_ACCUMULATORS / 32);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -287,9 +287,13 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                     b_hi[ct + T_CONVERTERS * i] = h;
                     b_lo[ct + T_CONVERTERS * i] = l;
                 }
-                mbar_arrive(raw_empty(rs)); // the raw stage has been read: TMA may refill it
-                fence_async_smem();         // the converted tiles are read by the tensor core (async proxy)
-                mbar_arrive(cvt_full(cs));
+                fence_async_smem(); // the converted tiles are read by the tensor core (async proxy)
+                __syncwarp();
+                if(lane == 0) // one arrival per warp: 256 arrivals on one barrier word would serialise
+                {
+                    mbar_arrive(raw_empty(rs)); // the raw stage has been read: TMA may refill it
+                    mbar_arrive(cvt_full(cs));
+                }
             }
         }
     }
@@ -383,7 +387,9 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(acc_empty(buf));
+                __syncwarp();
+                if(lane == 0)
+                    mbar_arrive(acc_empty(buf));
             }
             if(!ok)
                 break;
