@@ -7,21 +7,22 @@
 //   a = a_hi + a_lo,  a_hi = tf32(a),  a_lo = tf32(a - a_hi)          (both round-to-nearest)
 //   A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi                          (three tensor-core products)
 //
-// Kernel: one persistent CTA per SM, 128 x 128 tiles, K blocks of 32 floats (= one 128-byte swizzle row).
-//   warp 16     TMA producer: cp.async.bulk.tensor.2d of the raw FP32 A and B tiles (K-major, 128B swizzle)
-//               into a ring of raw stages
-//   warps 8-15  converters: read a raw stage, write the hi and lo halves of both tiles into a ring of
-//               converted stages (elementwise and position preserving, so the swizzled placement stays
-//               valid), fence to the async proxy, release the raw stage
-//   warp 17     one thread issues tcgen05.mma.kind::tf32 (M=128, N=128, K=8), 12 per K block, into one of
-//               two accumulators in tensor memory; tcgen05.commit releases the converted stage and, every
-//               T_CHUNK K blocks, publishes the partial sum
-//   warps 0-7   accumulate + epilogue: tcgen05.ld the finished partial sum (warp w owns TMEM lanes
-//               32*(w%4).. = tile rows, and columns 64*(w/4)..), add it to register accumulators, store C
-//               at the end of the tile.  The tensor core adds into its FP32 accumulator with truncation,
-//               which biases long sums (measured: error growing linearly with K, 2.4e-5 at K = 1024); moving
-//               the sum to registers (round-to-nearest adds) every 64 k keeps the error at about 1.7e-6
-//               for every K.
+// Kernel: one persistent CTA per SM (16 warps), 128 x 256 tiles, K blocks of 16 floats (= one 64-byte swizzle row),
+// a ring of four 48 KB stages [A raw][B raw][A lo][B lo].
+//   warp 12        TMA producer: cp.async.bulk.tensor.2d of the raw FP32 A and B tiles (K-major, 64B swizzle)
+//   warps 8-11,14-15  converters.  The tensor core ignores the low 13 mantissa bits of an FP32 word it reads as
+//                  TF32, so the raw tile is the hi half as it lies; the converters write lo = tf32(x - hi) at the
+//                  same offset of a second buffer (elementwise, so the swizzled placement holds for both) and
+//                  fence to the async proxy
+//   warp 13        one thread issues tcgen05.mma.kind::tf32 (M=128, N=256, K=8), 6 per K block, into one of two
+//                  accumulators in tensor memory (all 512 columns); tcgen05.commit releases the stage and, every
+//                  T_CHUNK K blocks, publishes the partial sum
+//   warps 0-7      accumulate + epilogue: tcgen05.ld the finished partial sum (warp w owns TMEM lanes 32*(w%4)..
+//                  = tile rows, and columns 128*(w/4)..), add it to 128 register accumulators per thread, store C
+//                  at the end of the tile.  The tensor core adds into its FP32 accumulator with truncation, which
+//                  biases long sums (measured: error growing linearly with K, 2.4e-5 at K = 1024); moving the sum
+//                  to registers (round-to-nearest adds) every 64 k keeps the error at about 1.7e-6 for every K.
+//                  These warps get their registers from a converter warpgroup (setmaxnreg, see T_LAUNCH_REGS).
 // Operands must be K-contiguous for this kernel (A row-major, B col-major); the host entry repacks the
 // other layouts (and operands whose pitch is not a multiple of 16 bytes) into a scratch arena first.
 // Every mbarrier wait is bounded; on a time-out the CTA records a status word, stops and frees its TMEM.
@@ -39,13 +40,23 @@ namespace
 using namespace sgemm_b200;
 
 constexpr int T_BM           = 128;
-constexpr int T_BK           = 32;  // floats: 128 bytes, one swizzle row
+constexpr int T_BK           = 16;  // floats: 64 bytes, one swizzle row
 constexpr int T_ACCUMULATORS = 256; // warps 0-7
-constexpr int T_CONVERTERS   = 256; // warps 8-15
-constexpr int T_TMA_WARP     = 16;
-constexpr int T_MMA_WARP     = 17;
-constexpr int T_THREADS      = 576;
-constexpr int T_CHUNK        = 2;  // K blocks accumulated inside the tensor core before the sum moves to registers
+constexpr int T_CONVERTERS   = 192; // warps 8-11 and 14-15
+constexpr int T_TMA_WARP     = 12;
+constexpr int T_MMA_WARP     = 13;
+constexpr int T_THREADS      = 512;
+// Register budget.  A launch of 512 threads gets 128 registers per thread (the whole file of 65 536).  The accumulate
+// warps keep 128 partial sums per thread, so one converter warpgroup hands registers over (setmaxnreg works on whole
+// warpgroups): 256 x 168 (warps 0-7) + 128 x 48 (warps 8-11) + 128 x 128 (warps 12-15, unchanged) = 65 536, exactly
+// the launch allocation, so the increase can always be granted.  The host refuses to launch a build whose kernel
+// was given fewer than T_LAUNCH_REGS registers.
+constexpr int T_LAUNCH_REGS  = 128;
+constexpr int T_ACC_REGS     = 168;
+constexpr int T_CVT_REGS     = 48;
+static_assert(T_ACCUMULATORS * T_ACC_REGS + 128 * T_CVT_REGS + 128 * T_LAUNCH_REGS == T_THREADS * T_LAUNCH_REGS,
+              "register budgets must add up to the launch allocation");
+constexpr int T_CHUNK        = 4;  // K blocks accumulated inside the tensor core before the sum moves to registers
 constexpr int T_ERR_WAIT     = 16; // status bit: a wait in this kernel timed out; bits 8..13 say which one first
 
 __device__ int g_tf32_status;
@@ -53,17 +64,16 @@ __device__ int g_tf32_status;
 template<int BN>
 struct TLayout
 {
-    static constexpr int    A_BYTES    = T_BM * T_BK * 4; // 16 KB
-    static constexpr int    B_BYTES    = BN * T_BK * 4;
-    static constexpr int    RAW_BYTES  = A_BYTES + B_BYTES;       // what TMA delivers per K block
-    static constexpr int    CVT_BYTES  = 2 * (A_BYTES + B_BYTES); // hi + lo halves of both tiles
-    static constexpr int    CVT_STAGES = 2;
-    static constexpr int    RAW_STAGES = (224 * 1024 - CVT_STAGES * CVT_BYTES) / RAW_BYTES;
-    static constexpr int    BARRIERS   = 2 * RAW_STAGES + 2 * CVT_STAGES + 4;
-    static constexpr size_t SMEM_BYTES = size_t(RAW_STAGES) * RAW_BYTES + size_t(CVT_STAGES) * CVT_BYTES
-                                         + 1024 /*alignment slack*/ + 256 /*barriers, TMEM address, abort flag*/;
-    static constexpr int    TMEM_COLS  = 2 * BN; // two partial accumulators
+    static constexpr int    A_BYTES     = T_BM * T_BK * 4; // 8 KB
+    static constexpr int    B_BYTES     = BN * T_BK * 4;   // 16 KB at BN = 256
+    static constexpr int    STAGE_BYTES = 2 * (A_BYTES + B_BYTES); // raw (= hi) and lo halves of both tiles
+    static constexpr int    STAGES      = (200 * 1024) / STAGE_BYTES;
+    static constexpr int    BARRIERS    = 3 * STAGES + 4;
+    static constexpr size_t SMEM_BYTES  = size_t(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/
+                                         + 256 /*barriers, TMEM address, abort flag*/;
+    static constexpr int    TMEM_COLS   = 2 * BN; // two partial accumulators
     static_assert(8 * BARRIERS + 16 <= 256, "barrier area");
+    static_assert(TMEM_COLS <= 512, "tensor memory has 512 columns");
 };
 
 struct TArgs
@@ -118,13 +128,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte swizzle:
-// start address (16-byte units), leading byte offset (unused for this layout, 1), stride byte offset =
-// 1024 bytes between groups of eight rows, descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr)
+// Shared-memory matrix descriptor of a K-major tile stored as rows of T_BK floats (64 bytes) with the 64-byte
+// swizzle: start address (16-byte units), leading byte offset (unused for this layout, 1), stride byte offset =
+// 512 bytes between groups of eight rows, descriptor version 1, layout type 4 (SWIZZLE_64B).
+__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr)
 {
-    return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46)
-           | (uint64_t(2) << 61);
+    static_assert(T_BK * 4 == 64, "descriptor written for 64-byte rows");
+    return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(512 >> 4) << 32) | (uint64_t(1) << 46)
+           | (uint64_t(4) << 61);
 }
 // Instruction descriptor: FP32 accumulator, TF32 A and B, both K-major, N >> 3, M >> 4.
 template<int BN>
@@ -132,11 +143,13 @@ __device__ __forceinline__ constexpr uint32_t umma_idesc_tf32()
 {
     return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(BN >> 3) << 17) | (uint32_t(T_BM >> 4) << 24);
 }
-// Round-to-nearest TF32 (10 mantissa bits) with integer instructions: measured 9 % faster for the whole
-// kernel than cvt.rna.tf32.f32, whose issue rate is lower; the results are identical except on ties.
-__device__ __forceinline__ float to_tf32(float x)
+// lo half of x for a hi half that is x with its low 13 mantissa bits dropped (what the tensor core sees when it reads
+// the raw word): x - hi is exact in FP32; it is rounded to nearest TF32 with integer instructions (measured 9 %
+// faster for the whole kernel than cvt.rna.tf32.f32, whose issue rate is lower).
+__device__ __forceinline__ float lo_half(float x)
 {
-    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+    const float hi = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+    return __uint_as_float((__float_as_uint(x - hi) + 0x1000u) & 0xFFFFE000u);
 }
 
 // Tile order: bands of 16 tile rows, tile columns advancing inside a band, so that the CTAs running at the same
@@ -157,36 +170,30 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                         const __grid_constant__ CUtensorMap map_b)
 {
     using L = TLayout<BN>;
-    constexpr int RAW = L::RAW_STAGES, CVT = L::CVT_STAGES;
+    constexpr int STAGES = L::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr  = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t tile_base = (raw_addr + 1023u) & ~1023u;
     uint8_t*       tiles     = smem_raw + (tile_base - raw_addr);
-    // [RAW raw stages: A, B as TMA wrote them][CVT converted stages: A_hi, A_lo, B_hi, B_lo][barriers]
-    const uint32_t cvt_base = tile_base + RAW * L::RAW_BYTES;
-    const uint32_t bar_base = cvt_base + CVT * L::CVT_BYTES;
+    // stage: [A as TMA wrote it = hi half][B likewise][A lo half][B lo half]; then the barriers
+    const uint32_t bar_base = tile_base + STAGES * L::STAGE_BYTES;
     auto raw_full  = [&](int s) { return bar_base + 8u * s; };
-    auto raw_empty = [&](int s) { return bar_base + 8u * (RAW + s); };
-    auto cvt_full  = [&](int s) { return bar_base + 8u * (2 * RAW + s); };
-    auto cvt_empty = [&](int s) { return bar_base + 8u * (2 * RAW + CVT + s); };
-    auto acc_full  = [&](int b) { return bar_base + 8u * (2 * RAW + 2 * CVT + b); };
-    auto acc_empty = [&](int b) { return bar_base + 8u * (2 * RAW + 2 * CVT + 2 + b); };
-    uint8_t*      misc       = tiles + RAW * L::RAW_BYTES + CVT * L::CVT_BYTES + 8 * (2 * RAW + 2 * CVT + 4);
+    auto cvt_full  = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto empty     = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto acc_full  = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };
+    auto acc_empty = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 + b); };
+    uint8_t*      misc       = tiles + STAGES * L::STAGE_BYTES + 8 * L::BARRIERS;
     uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(misc + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if(threadIdx.x == 0)
     {
-        for(int s = 0; s < RAW; ++s)
+        for(int s = 0; s < STAGES; ++s)
         {
             mbar_init(raw_full(s), 1);
-            mbar_init(raw_empty(s), T_CONVERTERS / 32);
-        }
-        for(int s = 0; s < CVT; ++s)
-        {
             mbar_init(cvt_full(s), T_CONVERTERS / 32);
-            mbar_init(cvt_empty(s), 1);
+            mbar_init(empty(s), 1);
         }
         for(int b = 0; b < 2; ++b)
         {
@@ -227,73 +234,55 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                 tile_coords(tile, t.tiles_m, t.tiles_n, tm, tn);
                 for(int kb = 0; kb < kblocks; ++kb, ++it)
                 {
-                    const int      s  = it % RAW;
-                    const uint32_t ph = (it / RAW) & 1;
-                    if(!mbar_wait(raw_empty(s), ph ^ 1, abort_flag)) { fail(0); ok = false; break; }
-                    const uint32_t st = tile_base + s * L::RAW_BYTES;
-                    mbar_arrive_expect_tx(raw_full(s), L::RAW_BYTES);
+                    const int      s  = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if(!mbar_wait(empty(s), ph ^ 1, abort_flag)) { fail(0); ok = false; break; }
+                    const uint32_t st = tile_base + s * L::STAGE_BYTES;
+                    mbar_arrive_expect_tx(raw_full(s), L::A_BYTES + L::B_BYTES);
                     tma_load_2d(st, &map_a, kb * T_BK, tm * T_BM, raw_full(s));
                     tma_load_2d(st + L::A_BYTES, &map_b, kb * T_BK, tn * BN, raw_full(s));
                 }
             }
         }
     }
-    else if(warp >= T_ACCUMULATORS / 32 && warp < T_TMA_WARP)
+    else if(warp >= T_ACCUMULATORS / 32 && warp != T_MMA_WARP)
     {
-        // ---------------- converters: raw FP32 -> hi and lo TF32 halves ----------------
-        // Elementwise and position preserving, so the 128-byte swizzle TMA applied stays valid for both halves.
-        const int ct = threadIdx.x - T_ACCUMULATORS;
+        // ---------------- converters: lo half of the raw tiles ----------------
+        if(warp < T_TMA_WARP) // the whole warpgroup 8-11 gives registers up; warps 14-15 keep theirs
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(T_CVT_REGS));
+        // The tensor core ignores the low 13 mantissa bits of an FP32 word it reads as TF32, so the raw tile IS the
+        // hi half (hi = the word truncated).  The converters add the lo half, lo = tf32(x - hi), elementwise and at
+        // the same offset in a second buffer, so the swizzled placement TMA applied holds for both.
+        const int ct = warp < T_TMA_WARP ? threadIdx.x - T_ACCUMULATORS : threadIdx.x - T_ACCUMULATORS - 64;
         uint32_t  it = 0;
         bool      ok = true;
         for(int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x)
         {
             for(int kb = 0; kb < kblocks; ++kb, ++it)
             {
-                const int      rs = it % RAW, cs = it % CVT;
-                const uint32_t rph = (it / RAW) & 1, cph = (it / CVT) & 1;
-                if(!mbar_wait(raw_full(rs), rph, abort_flag)) { fail(1); ok = false; break; }
-                if(!mbar_wait(cvt_empty(cs), cph ^ 1, abort_flag)) { fail(2); ok = false; break; }
-                const float4* raw = reinterpret_cast<const float4*>(tiles + rs * L::RAW_BYTES);
-                uint8_t*      cv  = tiles + RAW * L::RAW_BYTES + cs * L::CVT_BYTES;
-                float4*       a_hi = reinterpret_cast<float4*>(cv);
-                float4*       a_lo = reinterpret_cast<float4*>(cv + L::A_BYTES);
-                float4*       b_hi = reinterpret_cast<float4*>(cv + 2 * L::A_BYTES);
-                float4*       b_lo = reinterpret_cast<float4*>(cv + 2 * L::A_BYTES + L::B_BYTES);
-                constexpr int NA = L::A_BYTES / 16 / T_CONVERTERS, NB = L::B_BYTES / 16 / T_CONVERTERS;
-                float4        v[NA + NB];
+                const int      s  = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if(!mbar_wait(raw_full(s), ph, abort_flag)) { fail(1); ok = false; break; }
+                const float4* raw = reinterpret_cast<const float4*>(tiles + s * L::STAGE_BYTES);
+                float4*       lo  = reinterpret_cast<float4*>(tiles + s * L::STAGE_BYTES + L::A_BYTES + L::B_BYTES);
+                constexpr int NV = (L::A_BYTES + L::B_BYTES) / 16 / T_CONVERTERS; // 16-byte chunks per thread
+                static_assert(NV * T_CONVERTERS * 16 == L::A_BYTES + L::B_BYTES && NV % 4 == 0, "converter split");
 #pragma unroll
-                for(int i = 0; i < NA; ++i)
-                    v[i] = raw[ct + T_CONVERTERS * i];
-#pragma unroll
-                for(int i = 0; i < NB; ++i)
-                    v[NA + i] = raw[L::A_BYTES / 16 + ct + T_CONVERTERS * i];
-                auto split = [](const float4& x, float4& h, float4& l) {
-                    h.x = to_tf32(x.x); h.y = to_tf32(x.y); h.z = to_tf32(x.z); h.w = to_tf32(x.w);
-                    l.x = to_tf32(x.x - h.x); l.y = to_tf32(x.y - h.y); l.z = to_tf32(x.z - h.z); l.w = to_tf32(x.w - h.w);
-                };
-#pragma unroll
-                for(int i = 0; i < NA; ++i)
+                for(int r = 0; r < NV; r += 4) // four loads in flight at a time: fits the reduced register budget
                 {
-                    float4 h, l;
-                    split(v[i], h, l);
-                    a_hi[ct + T_CONVERTERS * i] = h;
-                    a_lo[ct + T_CONVERTERS * i] = l;
-                }
+                    float4 v[4];
 #pragma unroll
-                for(int i = 0; i < NB; ++i)
-                {
-                    float4 h, l;
-                    split(v[NA + i], h, l);
-                    b_hi[ct + T_CONVERTERS * i] = h;
-                    b_lo[ct + T_CONVERTERS * i] = l;
+                    for(int i = 0; i < 4; ++i)
+                        v[i] = raw[ct + T_CONVERTERS * (r + i)];
+#pragma unroll
+                    for(int i = 0; i < 4; ++i)
+                        lo[ct + T_CONVERTERS * (r + i)] =
+                            make_float4(lo_half(v[i].x), lo_half(v[i].y), lo_half(v[i].z), lo_half(v[i].w));
                 }
-                fence_async_smem(); // the converted tiles are read by the tensor core (async proxy)
+                fence_async_smem(); // the lo tiles are read by the tensor core (async proxy)
                 __syncwarp();
-                if(lane == 0) // one arrival per warp: 256 arrivals on one barrier word would serialise
-                {
-                    mbar_arrive(raw_empty(rs)); // the raw stage has been read: TMA may refill it
-                    mbar_arrive(cvt_full(cs));
-                }
+                if(lane == 0) // one arrival per warp
+                    mbar_arrive(cvt_full(s));
             }
         }
     }
@@ -318,24 +307,23 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                         tc_fence_after();
                     }
                     const uint32_t d  = tmem_base + buf * BN;
-                    const int      s  = it % CVT;
-                    const uint32_t ph = (it / CVT) & 1;
+                    const int      s  = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
                     if(!mbar_wait(cvt_full(s), ph, abort_flag)) { fail(4); ok = false; break; }
                     tc_fence_after();
-                    const uint32_t st   = cvt_base + s * L::CVT_BYTES;
-                    const uint32_t a_hi = st, a_lo = st + L::A_BYTES, b_hi = st + 2 * L::A_BYTES,
-                                   b_lo = st + 2 * L::A_BYTES + L::B_BYTES;
+                    const uint32_t st   = tile_base + s * L::STAGE_BYTES;
+                    const uint32_t a_hi = st, b_hi = st + L::A_BYTES, a_lo = b_hi + L::B_BYTES, b_lo = a_lo + L::A_BYTES;
 #pragma unroll
                     for(int kk = 0; kk < T_BK / 8; ++kk)
                     {
                         const uint32_t off = kk * 32; // 8 TF32 = 32 bytes along the swizzled row
-                        const uint64_t dah = umma_desc_k128(a_hi + off), dal = umma_desc_k128(a_lo + off);
-                        const uint64_t dbh = umma_desc_k128(b_hi + off), dbl = umma_desc_k128(b_lo + off);
+                        const uint64_t dah = umma_desc_kmajor(a_hi + off), dal = umma_desc_kmajor(a_lo + off);
+                        const uint64_t dbh = umma_desc_kmajor(b_hi + off), dbl = umma_desc_kmajor(b_lo + off);
                         tc_mma_tf32(d, dal, dbh, idesc, !(first && kk == 0));
                         tc_mma_tf32(d, dah, dbl, idesc, 1);
                         tc_mma_tf32(d, dah, dbh, idesc, 1);
                     }
-                    tc_commit(cvt_empty(s)); // the converted stage may be rewritten once these MMAs have read it
+                    tc_commit(empty(s)); // the stage may be refilled once these MMAs have read it
                     if(kb % T_CHUNK == T_CHUNK - 1 || kb == kblocks - 1)
                     {
                         tc_commit(acc_full(buf)); // the partial sum is complete once every MMA above has finished
@@ -352,6 +340,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         // (w/4)*BN/2..).  The tensor core adds into its FP32 accumulator with truncation, which biases long
         // sums; so the MMA warp starts a fresh TMEM accumulator every T_CHUNK K blocks and these warps add
         // the finished partial sums in registers with round-to-nearest.
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(T_ACC_REGS));
         constexpr int HALF = BN / 2;
         const int     q = warp & 3, h = warp >> 2;
         uint32_t      ccount = 0;
@@ -361,7 +350,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         {
             int tm, tn;
             tile_coords(tile, t.tiles_m, t.tiles_n, tm, tn);
-            float     acc[HALF];
+            float acc[HALF];
             for(int ch = 0; ch < chunks; ++ch, ++ccount)
             {
                 const uint32_t buf = ccount & 1, aph = (ccount >> 1) & 1;
@@ -492,7 +481,7 @@ EncodeFn encoder()
     return fn;
 }
 
-// rows x K operand, K contiguous, pitch ld floats; box = 32 floats x box_rows rows, 128-byte swizzle
+// rows x K operand, K contiguous, pitch ld floats; box = T_BK floats (64 bytes) x box_rows rows, 64-byte swizzle
 bool encode_kmajor(CUtensorMap* map, const float* base, size_t rows, size_t K, size_t ld, int box_rows)
 {
     EncodeFn fn = encoder();
@@ -503,7 +492,7 @@ bool encode_kmajor(CUtensorMap* map, const float* base, size_t rows, size_t K, s
     const cuuint32_t box[2]     = {(cuuint32_t)T_BK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2]    = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -542,6 +531,11 @@ int launch(Scratch& s, int which, const TArgs& t, const CUtensorMap& ma, const C
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TLayout<BN>::SMEM_BYTES);
         if(e != cudaSuccess)
             return (int)e;
+        cudaFuncAttributes fa;
+        if((e = cudaFuncGetAttributes(&fa, kernel)) != cudaSuccess)
+            return (int)e;
+        if(fa.numRegs < T_LAUNCH_REGS) // the register hand-over inside the kernel would not add up
+            return B200_SGEMM_NO_KERNEL;
         s.attr_set[which] = true;
     }
     const int tiles = t.tiles_m * t.tiles_n;
@@ -592,7 +586,7 @@ extern "C" int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float
     if((e = cudaPeekAtLastError()) != cudaSuccess)
         return (int)e;
 
-    const int bn = 128;
+    const int bn = 256;
     CUtensorMap ma, mb;
     if(!encode_kmajor(&ma, a_src, M, K, Kp, T_BM) || !encode_kmajor(&mb, b_src, N, K, Kp, bn))
         return B200_SGEMM_NO_KERNEL;
@@ -606,7 +600,7 @@ extern "C" int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float
     t.tiles_m  = (int)((M + T_BM - 1) / T_BM);
     t.tiles_n  = (int)((N + bn - 1) / bn);
     t.status   = s.status;
-    return launch<128>(s, 0, t, ma, mb, stream);
+    return launch<256>(s, 0, t, ma, mb, stream);
 }
 
 extern "C" int b200_sgemm_3xtf32_device_status(void)
