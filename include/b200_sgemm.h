@@ -159,7 +159,7 @@ int b200_sgemm_blas_shutdown(void);
 /* Optional comparison column, NOT part of the reference's surface and NOT its arithmetic: the same
  * C = A * B computed on the tensor cores (tcgen05, accumulators in tensor memory) with every FP32 operand
  * split into two TF32 halves and three products per pair ("3xTF32").  The result differs from the FP32 FMA
- * chain of b200_sgemm in the last few bits (relative error of a few 1e-7 against float64; identity B does not
+ * chain of b200_sgemm in the last few bits (relative error of about 2e-6 against float64; identity B does not
  * reproduce A bit for bit).  Same arguments as b200_sgemm.  Operands that are not K-contiguous (col-major A,
  * row-major B) or whose rows are not 16-byte aligned are first repacked into a per-device scratch arena
  * (first such call allocates; b200_sgemm_3xtf32_shutdown frees it).  b200_sgemm_3xtf32_device_status
