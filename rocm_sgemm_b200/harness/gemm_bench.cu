@@ -55,7 +55,7 @@ struct options
     std::vector<int> layouts{7, 3, 5, 1, 6, 2, 4, 0}; // the reference's registration order: ccc rcc crc rrc ccr rcr crr rrr
     int    batch_count = 1;
     int    iters = 100, warmup = 10;
-    bool   identity = false, json = false, vendor = true;
+    bool   identity = false, json = false, vendor = true, tf32x3 = false;
     size_t cpu_rows = 0;
 };
 
@@ -108,7 +108,8 @@ void usage(const char* prog)
                 "  --iters <n>         timed launches per row (default 100)   --warmup <n> (default 10)\n"
                 "  --identity          B = identity, verify C == A bit for bit\n"
                 "  --cpu <rows>        also time the host GEMM on <rows> rows of C\n"
-                "  --no-vendor         skip the cuBLAS column      --json   machine-readable rows\n",
+                "  --no-vendor         skip the cuBLAS column      --json   machine-readable rows\n"
+                "  --tf32x3            also time the optional 3xTF32 tensor-core entry (its own column)\n",
                 prog);
 }
 
@@ -160,6 +161,7 @@ int main(int argc, char** argv)
         else if(a == "--cpu") opt.cpu_rows = std::stoul(next());
         else if(a == "--json") opt.json = true;
         else if(a == "--no-vendor") opt.vendor = false;
+        else if(a == "--tf32x3") opt.tf32x3 = true;
         else if(a == "--help") { usage(argv[0]); return 0; }
         else std::fprintf(stderr, "ignoring unknown argument %s\n", a.c_str());
     }
@@ -181,8 +183,8 @@ int main(int argc, char** argv)
     {
         std::printf("device: %s, %d SMs, %.0f MHz, FP32 peak %.2f TFLOP/s\n", prop.name, prop.multiProcessorCount,
                     clock_khz * 1e-3, peak_tflops);
-        std::printf("%-44s %10s %10s %10s %11s %8s %12s %9s\n", "benchmark", "avg_ms", "min_ms", "max_ms", "avg_tflops",
-                    "%peak", "cublas_tflops", "vs_cublas");
+        std::printf("%-44s %10s %10s %10s %11s %8s %12s %9s%s\n", "benchmark", "avg_ms", "min_ms", "max_ms", "avg_tflops",
+                    "%peak", "cublas_tflops", "vs_cublas", opt.tf32x3 ? " tf32x3_tflops" : "");
     }
 
     cudaStream_t stream;
@@ -239,6 +241,10 @@ int main(int argc, char** argv)
             if(opt.vendor)
                 vendor = time_launches([&] { b200_cublas_gemm_layout(lc, la, lb, dC, dA, dB, M, N, K, stream); }, stream,
                                        flops, opt.warmup, opt.iters);
+            stats tensor; // the optional 3xTF32 tensor-core entry: its own column, not the graded arithmetic
+            if(opt.tf32x3)
+                tensor = time_launches([&] { b200_sgemm_3xtf32(lc, la, lb, dC, dA, dB, M, N, K, stream); }, stream, flops,
+                                       opt.warmup, opt.iters);
             char name[96];
             std::snprintf(name, sizeof name, "{A:%s,B:%s,C:%s,m:%zu,n:%zu,k:%zu}", layout_letter((layout)la),
                           layout_letter((layout)lb), layout_letter((layout)lc), M, N, K);
@@ -247,16 +253,20 @@ int main(int argc, char** argv)
                 std::printf("{\"name\":\"%s\",\"M\":%zu,\"N\":%zu,\"K\":%zu,\"layout\":\"%s%s%s\",\"avg_ms\":%.5f,"
                             "\"min_ms\":%.5f,\"max_ms\":%.5f,\"avg_tflops\":%.3f,\"min_time_tflops\":%.3f,"
                             "\"pct_fp32_peak\":%.2f,\"bytes_per_second\":%.4g,\"cublas_avg_tflops\":%.3f,"
-                            "\"cublas_min_ms\":%.5f,\"identity_exact\":%s}\n",
+                            "\"cublas_min_ms\":%.5f,\"tf32x3_avg_tflops\":%.3f,\"identity_exact\":%s}\n",
                             name, M, N, K, layout_letter((layout)la), layout_letter((layout)lb), layout_letter((layout)lc),
                             ours.avg_ms, ours.min_ms, ours.max_ms, ours.avg_tflops, flops / (ours.min_ms * 1e-3) * 1e-12,
                             100.0 * ours.avg_tflops / peak_tflops, bytes_per_s, vendor.avg_tflops, vendor.min_ms,
-                            opt.identity ? (exact ? "true" : "false") : "null");
+                            tensor.avg_tflops, opt.identity ? (exact ? "true" : "false") : "null");
             else
-                std::printf("%-44s %10.4f %10.4f %10.4f %11.2f %7.1f%% %12.2f %8.3fx%s\n", name, ours.avg_ms, ours.min_ms,
+            {
+                std::printf("%-44s %10.4f %10.4f %10.4f %11.2f %7.1f%% %12.2f %8.3fx", name, ours.avg_ms, ours.min_ms,
                             ours.max_ms, ours.avg_tflops, 100.0 * ours.avg_tflops / peak_tflops, vendor.avg_tflops,
-                            vendor.avg_tflops > 0 ? ours.avg_tflops / vendor.avg_tflops : 0.0,
-                            opt.identity ? (exact ? "  C==A" : "  C!=A (FAILED)") : "");
+                            vendor.avg_tflops > 0 ? ours.avg_tflops / vendor.avg_tflops : 0.0);
+                if(opt.tf32x3)
+                    std::printf(" %13.2f", tensor.avg_tflops);
+                std::printf("%s\n", opt.identity ? (exact ? "  C==A" : "  C!=A (FAILED)") : "");
+            }
             std::fflush(stdout);
             CUDA_CHECK(cudaFree(dA));
             CUDA_CHECK(cudaFree(dB));

@@ -39,11 +39,13 @@ def parse_rows(text: str):
     return rows
 
 
-def run_gemm_bench(shapes: str, iters: int, warmup: int, exe: Path | None = None) -> str:
+def run_gemm_bench(shapes: str, iters: int, warmup: int, exe: Path | None = None, tf32x3: bool = False) -> str:
     exe = exe or PKG / "bin" / "gemm_bench"
     if not exe.exists():
         raise RuntimeError(f"{exe} is missing: run python -m rocm_sgemm_b200.build first")
     cmd = [str(exe), "--json", "--shapes", shapes, "--iters", str(iters), "--warmup", str(warmup)]
+    if tf32x3:
+        cmd.append("--tf32x3")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=1800)
     if r.returncode != 0:
         raise RuntimeError(f"gemm_bench failed ({r.returncode}): {r.stderr[-2000:]}")
@@ -93,6 +95,23 @@ def markdown(rows, title: str, system: str = "", peak_tflops: float | None = Non
             if pc is None and pr is None:
                 continue
             out.append(f"| {name} | ({la},{lb}) | {_fmt(pc, '.1f')} | {_fmt(pr, '.1f')} |")
+    tensor = defaultdict(dict)
+    for r in rows:
+        if r.get("tf32x3_avg_tflops"):
+            tensor[(r["M"], r["N"], r["K"])][tuple(r["layout"])] = r["tf32x3_avg_tflops"]
+    if tensor:
+        out += ["", "## Optional 3xTF32 tensor-core column (`b200_sgemm_3xtf32`, not the FP32 FMA arithmetic)", ""]
+        out.append("| Matrix Size | Input Layout (A,B) | C=col | C=row | C=row / `b200_sgemm` |")
+        out.append("|:---|:---|---:|---:|---:|")
+        for size in sorted(tensor):
+            name = "x".join(str(d) for d in size)
+            for la, lb in LAYOUT_ORDER:
+                tc, tr = tensor[size].get((la, lb, "c")), tensor[size].get((la, lb, "r"))
+                if tc is None and tr is None:
+                    continue
+                base = ours[size].get((la, lb, "r"))
+                out.append(f"| {name} | ({la},{lb}) | {_fmt(tc, '.2f')} | {_fmt(tr, '.2f')} "
+                           f"| {_fmt(tr / base if tr and base else None, '.2f')} |")
     return "\n".join(out) + "\n"
 
 
@@ -103,13 +122,15 @@ def main(argv=None):
     ap.add_argument("--shapes", default="1024:2048:4096:8192")
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--tf32x3", action="store_true", help="with --run: also time the optional 3xTF32 entry")
     ap.add_argument("--title", default="Square matrices")
     ap.add_argument("--system", default="NVIDIA B200 (sm_100a), CUDA 12.9")
     ap.add_argument("--peak", type=float, default=74.45, help="FP32 FMA peak in TFLOP/s quoted in the second table")
+    ap.add_argument("--note", default="", help="text inserted under the title ('\\n' for line breaks)")
     ap.add_argument("--output", default="-")
     a = ap.parse_args(argv)
     if a.run:
-        text = run_gemm_bench(a.shapes, a.iters, a.warmup)
+        text = run_gemm_bench(a.shapes, a.iters, a.warmup, tf32x3=a.tf32x3)
     elif a.rows in (None, "-"):
         text = sys.stdin.read()
     else:
@@ -118,6 +139,9 @@ def main(argv=None):
     if not rows:
         raise SystemExit("no gemm_bench rows found")
     md = markdown(rows, a.title, a.system, a.peak)
+    if a.note:  # free text (for instance the commands that produced the rows) placed under the title
+        head, rest = md.split("\n", 1)
+        md = head + "\n\n" + a.note.replace("\\n", "\n") + "\n" + rest
     if a.output == "-":
         sys.stdout.write(md)
     else:

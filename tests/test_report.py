@@ -44,3 +44,14 @@ def test_cli_roundtrip(tmp_path):
     out = tmp_path / "r.md"
     report.main([str(src), "--output", str(out), "--title", "T"])
     assert out.read_text().startswith("# T\n")
+
+
+def test_tensor_core_column_is_a_separate_table():
+    base = json.loads(_row(4096, "rcr", 64.0, 57.0))
+    base["tf32x3_avg_tflops"] = 224.0
+    md = report.markdown(report.parse_rows(json.dumps(base)), "t")
+    assert "## Optional 3xTF32 tensor-core column" in md
+    line = [l for l in md.splitlines() if l.startswith("| 4096x4096x4096 | (r,c) | - | 224.00")][0]
+    assert line.endswith("| 3.50 |")
+    # rows without the key leave the report as it was
+    assert "3xTF32" not in report.markdown(report.parse_rows(_row(4096, "rcr", 64.0, 57.0)), "t")
