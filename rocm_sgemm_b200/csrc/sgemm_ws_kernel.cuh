@@ -116,9 +116,14 @@ struct WsLayout
     static constexpr size_t SMEM_BYTES = TILE_BYTES + size_t(2 * Cfg::STAGES) * 8 + 16;
     static constexpr int    PRODUCERS  = ws_producer_threads(Cfg::BLOCK_SIZE);
     static constexpr int    THREADS    = Cfg::BLOCK_SIZE + PRODUCERS;
-    // k-steps unrolled back to back.  The whole K tile for the 8x8 thread tile; larger thread tiles are
-    // unrolled 8 deep so that the loop body stays within a few KB of instructions.
-    static constexpr int    KU = (Cfg::TMT * Cfg::TNT > 64 && Cfg::BK > 8) ? 8 : Cfg::BK;
+    // k-steps unrolled back to back: the whole K tile.  A shallower unroll (compile with -DWS_KU_FORCE=8 or 16)
+    // keeps the loop body of the 128-accumulator thread tiles small but measured slower on B200
+    // (16x8 tile at 8192^3: 58.3 / 60.1 / 63.3 TFLOP/s for 8 / 16 / 32 steps).
+#ifdef WS_KU_FORCE
+    static constexpr int    KU = (Cfg::TMT * Cfg::TNT > 64 && Cfg::BK > WS_KU_FORCE) ? WS_KU_FORCE : Cfg::BK;
+#else
+    static constexpr int    KU = Cfg::BK;
+#endif
     // Thread tiles of 128 accumulators need more registers than an even split of the register file
     // gives 8 consumer + 4 producer warps.  Both groups are whole warpgroups then, so the producers hand
     // registers over (setmaxnreg).  The two budgets add up to exactly what the launch allocated,
