@@ -77,6 +77,18 @@ int b200_sgemm_ex(int layout_c, int layout_a, int layout_b, float* C, const floa
                   size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant, int split_k, void* workspace,
                   size_t workspace_bytes, void* cuda_stream);
 
+/* The product written to several destinations at once: C_list[0 .. n_dst-1] (1 <= n_dst <= 8) all receive the
+ * M x N result with the same layout and leading dimension; the kernel's epilogue stores every tile to each of them.
+ * Meant for the column-sharded multi-GPU product: each GPU passes the position of its own column block inside its
+ * own C and inside every peer's C (peer mappings obtained with CUDA IPC or any other peer-access mechanism), so that
+ * when all GPUs have finished every GPU holds the whole C and the all-gather that would follow
+ * (the reference has no multi-GPU path; its matrices live on one device, test/gemm/test.cpp:50-74) is
+ * folded into the GEMM.  Plain stores only; the caller synchronises the GPUs before reading C.  Runs the
+ * warp-specialised kernels without split-K: B200_SGEMM_NO_KERNEL if `variant` (-1 = the table's) is another kind. */
+int b200_sgemm_multi(int layout_c, int layout_a, int layout_b, float* const* C_list, int n_dst, const float* A,
+                     const float* B, size_t M, size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant,
+                     void* cuda_stream);
+
 /* Bytes of split-K workspace b200_sgemm_ex needs for this call (0 when the effective split is 1). */
 size_t b200_sgemm_workspace_bytes(int layout_c, int layout_a, int layout_b, size_t M, size_t N, size_t K, int variant,
                                   int split_k);

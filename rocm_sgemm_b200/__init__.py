@@ -88,7 +88,7 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
            "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
-           "b200_sgemm_blas_shutdown")
+           "b200_sgemm_blas_shutdown", "b200_sgemm_multi")
 
 
 def lib() -> ctypes.CDLL:
@@ -116,7 +116,8 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_host.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz]
     l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_3xtf32.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _vp]
-    l.b200_sgemm_strided_batched.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _vp]
+    l.b200_sgemm_multi.argtypes = [i, i, i, ctypes.POINTER(_vp), i, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, i, _vp]
+    l.b200_sgemm_strided_batched.argtypes =[i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _vp]
     l.b200_sgemm_blas.argtypes = [i, i, _sz, _sz, _sz, ctypes.c_float, _vp, _sz, _vp, _sz, ctypes.c_float, _vp, _sz, _vp]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
@@ -187,6 +188,15 @@ def gemm_host(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int) -> 
     """C = A @ B for HOST matrices (raw addresses or tensors; page-locked for full speed): uploads, multiplies and
     downloads in one pipelined, blocking call (b200_sgemm_host)."""
     _check(lib().b200_sgemm_host(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K))
+
+
+def gemm_multi(layout_c, layout_a, layout_b, C_list, A, B, M: int, N: int, K: int, lda: int = 0, ldb: int = 0,
+               ldc: int = 0, variant: int = -1, stream=None) -> None:
+    """The product stored to every destination in C_list (tensors or raw device addresses, peer mappings included):
+    the epilogue of one kernel writes each tile to all of them (b200_sgemm_multi)."""
+    ptrs = (_vp * len(C_list))(*[_ptr(c) for c in C_list])
+    _check(lib().b200_sgemm_multi(int(layout_c), int(layout_a), int(layout_b), ptrs, len(C_list), _ptr(A), _ptr(B), M, N,
+                                  K, lda, ldb, ldc, variant, _stream(stream)))
 
 
 def gemm_strided_batched(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, stride_c: int, stride_a: int,

@@ -37,6 +37,7 @@ __host__ __device__ constexpr int ws_producer_threads(int consumer_threads)
 {
     return consumer_threads >= 256 ? 128 : 64;
 }
+constexpr int      WS_MAX_EXTRA     = 7; // peers of an 8-GPU node
 constexpr uint32_t WS_SPIN_LIMIT    = 1u << 22;
 constexpr uint64_t WS_WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull; // one second per wait
 
@@ -50,6 +51,11 @@ struct WsArgs
     int      total_units;  // tiles * splits
     int      tma_a, tma_b; // 1: the operand is fetched by TMA through the tensor map below
     int*     status;       // device status word
+    // Further destinations of the result (same leading dimension as C): the tile is stored to each of them as well.
+    // Used to write this GPU's block of C straight into the other GPUs' copies of C through peer mappings, which
+    // folds the all-gather that follows a column-sharded product into the epilogue.  Only without split-K.
+    int      n_extra;
+    float*   extra_c[WS_MAX_EXTRA];
 };
 
 // ---- mbarrier / TMA helpers ------------------------------------------------------------------------
@@ -454,6 +460,8 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     unpack2(acc2[i][j], c[i][2 * j], c[i][2 * j + 1]);
         }
         store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)split * p.split_stride, m0 + tm0, n0 + tn0);
+        for(int d = 0; d < w.n_extra; ++d) // plain stores; to a peer GPU's memory when the pointer is a peer mapping
+            store_tile<Cfg, LC, ALIGNED>(c, p, w.extra_c[d], m0 + tm0, n0 + tn0);
     }
 }
 

@@ -55,3 +55,83 @@ def all_gather_c(C_local, layout_c: int, M: int, N: int, world: int, group=None)
     full = torch.empty(world * C_local.numel(), dtype=C_local.dtype, device=C_local.device)
     dist.all_gather_into_tensor(full, C_local, group=group)
     return assemble_c(full, layout_c, M, N, world)
+
+
+def block_offset(layout_c: int, M: int, N: int, world: int, rank: int) -> tuple[int, int]:
+    """(element offset of rank's column block inside a full packed M x N matrix, leading dimension of that matrix).
+    Row-major C: the block starts at column rank*N/G of row 0, rows are N apart.  Col-major C: the block is the
+    contiguous range of its columns, columns are M apart."""
+    n0, _ = shard_columns(N, world, rank)
+    return (n0, N) if layout_c == ROW else (n0 * M, M)
+
+
+class _DeviceArray:
+    """Minimal __cuda_array_interface__ holder so that torch can view a raw device allocation."""
+
+    def __init__(self, ptr: int, numel: int):
+        self.__cuda_array_interface__ = {"shape": (numel,), "typestr": "<f4", "data": (int(ptr), False), "version": 3}
+
+
+class PeerGatheredC:
+    """A full-size C on every rank, each rank's copy mapped into all the other processes with CUDA IPC.
+
+    With these mappings the GEMM's epilogue (b200_sgemm_multi) stores this rank's column block into every copy, so
+    the all-gather that would follow the column-sharded product happens inside the kernel, over NVLink, tile by tile
+    while the FMAs of the other tiles run.  Plain peer stores only (no multicast objects); every rank must pass a
+    barrier after its kernel before anybody reads C, and before the buffers are closed.
+    """
+
+    def __init__(self, M: int, N: int, layout_c: int, world: int, rank: int, group=None):
+        import torch.distributed as dist
+        from cuda.bindings import runtime as rt
+        self._rt, self.M, self.N, self.layout_c, self.world, self.rank = rt, M, N, layout_c, world, rank
+        err, self.ptr = rt.cudaMalloc(M * N * 4)
+        if err != rt.cudaError_t.cudaSuccess:
+            raise RuntimeError(f"cudaMalloc failed: {err}")
+        err, handle = rt.cudaIpcGetMemHandle(self.ptr)
+        if err != rt.cudaError_t.cudaSuccess:
+            raise RuntimeError(f"cudaIpcGetMemHandle failed: {err}")
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle.reserved), group=group)
+        self.copies = []  # device address of every rank's C as seen from this process
+        for g in range(world):
+            if g == rank:
+                self.copies.append(int(self.ptr))
+                continue
+            h = rt.cudaIpcMemHandle_t()
+            h.reserved = handles[g]
+            err, p = rt.cudaIpcOpenMemHandle(h, rt.cudaIpcMemLazyEnablePeerAccess)
+            if err != rt.cudaError_t.cudaSuccess:
+                raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {g}: {err}")
+            self.copies.append(int(p))
+
+    def destinations(self) -> tuple[list[int], int]:
+        """(addresses of this rank's column block in its own copy first, then in every peer's copy; leading dimension)."""
+        off, ld = block_offset(self.layout_c, self.M, self.N, self.world, self.rank)
+        order = [self.rank] + [g for g in range(self.world) if g != self.rank]
+        return [self.copies[g] + 4 * off for g in order], ld
+
+    def tensor(self):
+        """This rank's full C as a 1-D torch tensor (a view of the raw allocation)."""
+        import torch
+        return torch.as_tensor(_DeviceArray(self.ptr, self.M * self.N), device="cuda")
+
+    def close(self, group=None):
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # nobody is still storing into a copy that is about to go away
+        for g, p in enumerate(self.copies):
+            if g != self.rank:
+                self._rt.cudaIpcCloseMemHandle(p)
+        dist.barrier(group=group)
+        self._rt.cudaFree(self.ptr)
+        self.copies = []
+
+
+def fused_gather_gemm(sg, peer_c: PeerGatheredC, layout_c: int, layout_a: int, layout_b: int, A, B_local, M: int, N: int,
+                      K: int, stream=None, variant: int = -1):
+    """This rank's M x N/G product stored straight into every rank's full C (sg = the rocm_sgemm_b200 module)."""
+    _, n = shard_columns(N, peer_c.world, peer_c.rank)
+    dsts, ldc = peer_c.destinations()
+    sg.gemm_multi(layout_c, layout_a, layout_b, dsts, A, B_local, M, n, K, ldc=ldc, variant=variant, stream=stream)

@@ -119,3 +119,30 @@ def test_blas_argument_errors(sgemm):
         sgemm.gemm_blas(1, 0, 8, 4, 8, 1.0, x, 8, x, 8, 0.0, x, 7)  # ldc < M
     with pytest.raises(sgemm.SgemmError):
         sgemm.gemm_blas(0, 0, 0, 8, 8, 1.0, x, 8, x, 8, 0.0, x, 8)
+
+
+@pytest.mark.parametrize("lc", [0, 1], ids=["Crow", "Ccol"])
+def test_multi_destination_store(sgemm, orc, lc):
+    """b200_sgemm_multi: one kernel stores the result to several destinations (here three column blocks of full-size
+    matrices on the same GPU, the single-GPU stand-in for the peers' copies of C)."""
+    from rocm_sgemm_b200 import sharded
+    M, N, K, world, rank = 192, 512, 96, 4, 2
+    n = N // world
+    la, lb = 1, 0
+    A, B = orc.fill_ab(50, la, lb, M, n, K)
+    full = [torch.full((M * N,), float("nan"), device="cuda") for _ in range(3)]
+    off, ld = sharded.block_offset(lc, M, N, world, rank)
+    dsts = [f.data_ptr() + 4 * off for f in full]
+    sgemm.gemm_multi(lc, la, lb, dsts, dev(A), dev(B), M, n, K, ldc=ld)
+    torch.cuda.synchronize()
+    # this entry never splits K: one FMA chain per element
+    want = as2d(orc.sgemm_fma(lc, la, lb, A, B, M, n, K, splits=1, threads=orc.max_threads()), lc, M, n)
+    for f in full:
+        got = as2d(f.cpu().numpy(), lc, M, N)
+        assert np.array_equal(bits(np.ascontiguousarray(got[:, rank * n:(rank + 1) * n])), bits(np.ascontiguousarray(want)))
+        rest = np.delete(got, np.s_[rank * n:(rank + 1) * n], axis=1)
+        assert np.isnan(rest).all()  # nothing outside the block is touched
+    with pytest.raises(sgemm.SgemmError):
+        sgemm.gemm_multi(lc, la, lb, [], dev(A), dev(B), M, n, K, ldc=ld)
+    with pytest.raises(sgemm.SgemmError):
+        sgemm.gemm_multi(lc, la, lb, [dsts[0]] * 9, dev(A), dev(B), M, n, K, ldc=ld)

@@ -78,3 +78,24 @@ def test_two_ranks_over_gloo():
     results = mgr.dict()
     mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
+
+
+def test_block_offset_matches_assembly():
+    """The offset / leading dimension that the fused epilogue stores with addresses the same elements as the
+    assembly of gathered blocks."""
+    import torch
+    from rocm_sgemm_b200 import sharded
+    M, N, world = 6, 8, 4
+    n = N // world
+    for lc in (0, 1):
+        full = torch.full((M * N,), -1.0)
+        blocks = []
+        for r in range(world):
+            blk = torch.arange(M * n, dtype=torch.float32) + 1000 * r
+            blocks.append(blk)
+            off, ld = sharded.block_offset(lc, M, N, world, r)
+            view = blk.view(M, n) if lc == 0 else blk.view(n, M)
+            for o in range(view.shape[0]):
+                full[off + o * ld: off + o * ld + view.shape[1]] = view[o]
+        want = sharded.assemble_c(torch.cat(blocks), lc, M, N, world)
+        assert torch.equal(full, want)
