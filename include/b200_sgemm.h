@@ -84,7 +84,9 @@ int b200_sgemm_ex(int layout_c, int layout_a, int layout_b, float* C, const floa
  * when all GPUs have finished every GPU holds the whole C and the all-gather that would follow
  * (the reference has no multi-GPU path; its matrices live on one device, test/gemm/test.cpp:50-74) is
  * folded into the GEMM.  Plain stores only; the caller synchronises the GPUs before reading C.  Runs the
- * warp-specialised kernels without split-K: B200_SGEMM_NO_KERNEL if `variant` (-1 = the table's) is another kind. */
+ * warp-specialised kernels without split-K: B200_SGEMM_NO_KERNEL if `variant` (-1 = the table's) is another kind.
+ * With variant = -1 the table entry may, as in b200_sgemm, pre-transpose a K-contiguous operand into the
+ * library's per-(device, stream) arena. */
 int b200_sgemm_multi(int layout_c, int layout_a, int layout_b, float* const* C_list, int n_dst, const float* A,
                      const float* B, size_t M, size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant,
                      void* cuda_stream);
