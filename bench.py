@@ -320,28 +320,32 @@ def ours(args, w):
     fused = None
     if world > 1:
         from rocm_sgemm_b200 import sharded
-        pc = sharded.PeerGatheredC(M, N, lc, G, rank)
-        for _ in range(2):
-            sharded.fused_gather_gemm(sg, pc, lc, la, lb, dA, dB, M, N, K, stream=stream)
-        barrier()
-        fsteps = max(3, min(args.steps, 10))
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for _ in range(fsteps):
-            sharded.fused_gather_gemm(sg, pc, lc, la, lb, dA, dB, M, N, K, stream=stream)
-        f1.record()
-        barrier()
-        tf = torch.tensor([f0.elapsed_time(f1) / fsteps], dtype=torch.float64, device=dev)
-        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
-        # every rank now holds the whole C: it must equal the NCCL all-gather of the separately computed blocks
-        same = torch.equal(pc.tensor().view(torch.int32), sharded.assemble_c(full, lc, M, N, G).view(torch.int32))
-        ts = torch.tensor([1.0 if same else 0.0], dtype=torch.float64, device=dev)
-        dist.all_reduce(ts, op=dist.ReduceOp.MIN)
-        fused = {"ms_per_step": tf.item(), "tflops": flops_total / (tf.item() * 1e-3) / 1e12,
-                 "gemm_then_nccl_allgather_ms": avg_ms + allgather_ms, "bit_identical_to_allgather": bool(ts.item()),
-                 "note": "b200_sgemm_multi: each rank's epilogue stores its column block into every rank's C (CUDA IPC "
-                         "peer mappings, plain stores); informational, not part of value"}
-        pc.close()
+        try:  # the constructor fails on all ranks or on none
+            pc = sharded.PeerGatheredC(M, N, lc, G, rank)
+        except RuntimeError as ex:
+            pc, fused = None, {"unavailable": str(ex)}
+        if pc is not None:
+            for _ in range(2):
+                sharded.fused_gather_gemm(sg, pc, lc, la, lb, dA, dB, M, N, K, stream=stream)
+            barrier()
+            fsteps = max(3, min(args.steps, 10))
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record()
+            for _ in range(fsteps):
+                sharded.fused_gather_gemm(sg, pc, lc, la, lb, dA, dB, M, N, K, stream=stream)
+            f1.record()
+            barrier()
+            tf = torch.tensor([f0.elapsed_time(f1) / fsteps], dtype=torch.float64, device=dev)
+            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+            # every rank now holds the whole C: it must equal the NCCL all-gather of the separately computed blocks
+            same = torch.equal(pc.tensor().view(torch.int32), sharded.assemble_c(full, lc, M, N, G).view(torch.int32))
+            ts = torch.tensor([1.0 if same else 0.0], dtype=torch.float64, device=dev)
+            dist.all_reduce(ts, op=dist.ReduceOp.MIN)
+            fused = {"ms_per_step": tf.item(), "tflops": flops_total / (tf.item() * 1e-3) / 1e12,
+                     "gemm_then_nccl_allgather_ms": avg_ms + allgather_ms, "bit_identical_to_allgather": bool(ts.item()),
+                     "note": "b200_sgemm_multi: each rank's epilogue stores its column block into every rank's C (CUDA IPC "
+                             "peer mappings, plain stores); informational, not part of value"}
+            pc.close()
         del full
 
     # ---- end to end: pinned host buffers -> device -> GEMM -> host, every step -------------------------

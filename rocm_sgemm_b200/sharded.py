@@ -85,15 +85,24 @@ class PeerGatheredC:
         import torch.distributed as dist
         from cuda.bindings import runtime as rt
         self._rt, self.M, self.N, self.layout_c, self.world, self.rank = rt, M, N, layout_c, world, rank
-        err, self.ptr = rt.cudaMalloc(M * N * 4)
-        if err != rt.cudaError_t.cudaSuccess:
-            raise RuntimeError(f"cudaMalloc failed: {err}")
-        err, handle = rt.cudaIpcGetMemHandle(self.ptr)
-        if err != rt.cudaError_t.cudaSuccess:
-            raise RuntimeError(f"cudaIpcGetMemHandle failed: {err}")
+        # Every step that can fail is followed by an exchange of its outcome, so that either all ranks end up with
+        # a working object or all of them raise: nobody is left waiting in a collective for a rank that gave up.
+        self.ptr, self.copies, why, mine = None, [], "", None
+        err, ptr = rt.cudaMalloc(M * N * 4)
+        if err == rt.cudaError_t.cudaSuccess:
+            self.ptr = ptr
+            err, handle = rt.cudaIpcGetMemHandle(self.ptr)
+            if err == rt.cudaError_t.cudaSuccess:
+                mine = bytes(handle.reserved)
+            else:
+                why = f"cudaIpcGetMemHandle failed: {err}"
+        else:
+            why = f"cudaMalloc failed: {err}"
         handles = [None] * world
-        dist.all_gather_object(handles, bytes(handle.reserved), group=group)
-        self.copies = []  # device address of every rank's C as seen from this process
+        dist.all_gather_object(handles, mine, group=group)
+        if any(h is None for h in handles):
+            self._release()
+            raise RuntimeError(why or "a peer could not export its copy of C")
         for g in range(world):
             if g == rank:
                 self.copies.append(int(self.ptr))
@@ -102,8 +111,25 @@ class PeerGatheredC:
             h.reserved = handles[g]
             err, p = rt.cudaIpcOpenMemHandle(h, rt.cudaIpcMemLazyEnablePeerAccess)
             if err != rt.cudaError_t.cudaSuccess:
-                raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {g}: {err}")
-            self.copies.append(int(p))
+                why = f"cudaIpcOpenMemHandle failed for rank {g}: {err}"
+                self.copies.append(0)
+            else:
+                self.copies.append(int(p))
+        outcomes = [None] * world
+        dist.all_gather_object(outcomes, why, group=group)
+        if any(outcomes):
+            self._release()
+            raise RuntimeError(next(o for o in outcomes if o))
+
+    def _release(self):
+        """Closes the peer mappings and frees this rank's copy; no collective inside."""
+        for g, p in enumerate(self.copies):
+            if g != self.rank and p:
+                self._rt.cudaIpcCloseMemHandle(p)
+        self.copies = []
+        if self.ptr is not None:
+            self._rt.cudaFree(self.ptr)
+            self.ptr = None
 
     def destinations(self) -> tuple[list[int], int]:
         """(addresses of this rank's column block in its own copy first, then in every peer's copy; leading dimension)."""
@@ -121,12 +147,11 @@ class PeerGatheredC:
         import torch.distributed as dist
         torch.cuda.synchronize()
         dist.barrier(group=group)  # nobody is still storing into a copy that is about to go away
-        for g, p in enumerate(self.copies):
-            if g != self.rank:
-                self._rt.cudaIpcCloseMemHandle(p)
+        ptr, self.ptr = self.ptr, None
+        self._release()            # peer mappings first ...
         dist.barrier(group=group)
-        self._rt.cudaFree(self.ptr)
-        self.copies = []
+        if ptr is not None:        # ... then the allocation they pointed into
+            self._rt.cudaFree(ptr)
 
 
 def fused_gather_gemm(sg, peer_c: PeerGatheredC, layout_c: int, layout_a: int, layout_b: int, A, B_local, M: int, N: int,
