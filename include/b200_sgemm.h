@@ -145,9 +145,17 @@ int b200_sgemm_device_status(int* status);
  * complete in host memory.  This is the sequence the reference's harness performs step by step
  * (test/gemm/test.cpp:50-74: hipMemcpy H2D, gemm, hipMemcpy D2H) folded into one call; page-locked host
  * buffers are needed for the overlap.  Device buffers come from a per-device arena of the library
- * (b200_sgemm_shutdown_host releases it).  Calls are serialised per process. */
+ * (b200_sgemm_shutdown_host releases it).
+ * b200_sgemm_host_submit only enqueues the job on the current device and returns a ticket; b200_sgemm_host_wait
+ * (same device current) blocks until that job's C is complete in host memory; the host buffers must stay valid and
+ * untouched in between.  Two jobs may be in flight per device (a third submit first waits for the oldest): the
+ * uploads of the next job then overlap the compute-bound tail and the downloads of the current one, so a stream
+ * of jobs runs at the pace of the uploads.  b200_sgemm_host = submit + wait. */
 int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
                     size_t N, size_t K);
+int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
+                           size_t N, size_t K, long long* ticket);
+int b200_sgemm_host_wait(long long ticket);
 int b200_sgemm_shutdown_host(void);
 
 /* The same product for `batch` matrices at fixed element strides: matrix b uses C + b*stride_c, A + b*stride_a,

@@ -85,7 +85,8 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_num_variants", "b200_sgemm_get_variant", "b200_sgemm_num_entries", "b200_sgemm_get_entry",
            "b200_sgemm_get_entry_pretranspose", "b200_sgemm_map_tile",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
-           "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
+           "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_host_submit", "b200_sgemm_host_wait",
+           "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
            "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
            "b200_sgemm_blas_shutdown", "b200_sgemm_multi")
@@ -114,6 +115,8 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_fma_peak.argtypes = [i, i, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double), _vp]
     l.b200_sgemm_device_status.argtypes = [ctypes.POINTER(i)]
     l.b200_sgemm_host.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz]
+    l.b200_sgemm_host_submit.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, ctypes.POINTER(ctypes.c_longlong)]
+    l.b200_sgemm_host_wait.argtypes = [ctypes.c_longlong]
     l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_3xtf32.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _vp]
     l.b200_sgemm_multi.argtypes = [i, i, i, ctypes.POINTER(_vp), i, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, i, _vp]
@@ -223,6 +226,20 @@ def gemm_3xtf32(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, s
 def tf32x3_device_status() -> int:
     """Synchronises the device; 0 unless a bounded wait inside the 3xTF32 kernel gave up."""
     return int(lib().b200_sgemm_3xtf32_device_status())
+
+
+def gemm_host_submit(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int) -> int:
+    """Enqueues the host-buffer GEMM and returns a ticket at once (b200_sgemm_host_submit).  Up to two jobs are in
+    flight per device; the host buffers must stay valid and untouched until gemm_host_wait(ticket) returns."""
+    t = ctypes.c_longlong(-1)
+    _check(lib().b200_sgemm_host_submit(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K,
+                                        ctypes.byref(t)))
+    return int(t.value)
+
+
+def gemm_host_wait(ticket: int) -> None:
+    """Blocks until the job behind `ticket` has its C complete in host memory."""
+    _check(lib().b200_sgemm_host_wait(int(ticket)))
 
 
 def workspace_bytes(layout_c, layout_a, layout_b, M, N, K, variant: int = -1, split_k: int = 0) -> int:

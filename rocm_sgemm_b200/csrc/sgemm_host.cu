@@ -1,7 +1,8 @@
-// b200_sgemm_host: the GEMM for callers whose matrices live in HOST memory.
+// b200_sgemm_host / b200_sgemm_host_submit / b200_sgemm_host_wait: the GEMM for callers whose matrices live in
+// HOST memory.
 //
 // The reference's harnesses copy A and B to the device, call gemm(), and copy C back, one step after the
-// other (test/gemm/test.cpp:50-74).  This entry does the same work end to end but overlaps the phases.
+// other (test/gemm/test.cpp:50-74).  These entries do the same work end to end but overlap the phases.
 // At 4096^3 the uploads (128 MiB over PCIe, about 2.4 ms) take longer than the GEMM (2.1 ms), so the aim
 // is to have as much of the product as possible computed while the operands are still arriving:
 //
@@ -10,16 +11,21 @@
 //     computable: A_k x (the B panels present) after A_k, (the A panels present) x B_k after B_k.  This
 //     order maximises the computable share of C at every moment of the upload (the product of the shares
 //     of A and B present is largest when the two are equal).
-//   * each strip is ONE GEMM launch on the device matrices (leading dimensions = the full ones), with a
-//     split-K factor chosen so that tiles x splits fills the SMs in whole waves;
+//   * each strip is ONE GEMM launch on the device matrices (leading dimensions = the full ones); strips
+//     rotate over several compute streams so that the persistent kernels of consecutive strips fill the
+//     SMs that the last wave of the previous one leaves idle;
 //   * each finished strip is downloaded while the next ones are uploaded and computed (the GPU's copy
 //     engines work in both directions at once).
 //
-// Streams (upload, several for compute, download) ordered by events; nothing is allocated once the buffers of
-// a problem size exist.  Host buffers should be page-locked (cudaHostAlloc / cudaHostRegister); pageable
-// memory works but the runtime then stages the copies and the overlap is lost.  The device buffers come
-// from a per-device arena owned by the library (grown on demand, released by b200_sgemm_shutdown_host).
-// The call returns after C is complete in host memory.
+// submit() only enqueues (copies, kernels, events) and returns a ticket; wait() blocks until that job's C is
+// complete in host memory.  Two jobs can be in flight per device (two sets of device matrices): the uploads of
+// job i+1 then run during the compute-bound second half and the downloads of job i, and a stream of jobs
+// proceeds at the pace of the uploads alone.  b200_sgemm_host() is submit() followed by wait().
+//
+// Host buffers should be page-locked (cudaHostAlloc / cudaHostRegister); pageable memory works but the runtime
+// then stages the copies and the overlap is lost.  They must stay untouched until wait() returns.  The device
+// buffers come from a per-device arena owned by the library (grown on demand, released by
+// b200_sgemm_shutdown_host).
 #include "../../include/b200_sgemm.h"
 
 #include <cuda_runtime.h>
@@ -28,27 +34,34 @@
 #include <map>
 #include <mutex>
 #include <vector>
-#ifdef B200_SGEMM_HOST_TRACE
-#include <cstdio>
-#include <cstdlib>
-#endif
 
 namespace
 {
-constexpr int MAX_PIECES = 8;              // per operand
-constexpr int MAX_STRIPS = 2 * MAX_PIECES; // one strip per upload at most
+constexpr int MAX_PIECES      = 8;              // per operand
+constexpr int MAX_STRIPS      = 2 * MAX_PIECES; // one strip per upload at most
 constexpr int COMPUTE_STREAMS = 4;
+constexpr int SLOTS           = 2;              // jobs in flight per device
+
+struct Slot
+{
+    float*      dA = nullptr;
+    float*      dB = nullptr;
+    float*      dC = nullptr;
+    size_t      bytesA = 0, bytesB = 0, bytesC = 0;
+    cudaEvent_t uploaded[MAX_STRIPS] = {};
+    cudaEvent_t computed[MAX_STRIPS] = {};
+    cudaEvent_t done = nullptr; // recorded on the download stream after the job's last copy
+    bool        busy = false;
+    long long   ticket = -1;
+};
 
 struct HostCtx
 {
-    float*       dA = nullptr;
-    float*       dB = nullptr;
-    float*       dC = nullptr;
-    float*       ws[COMPUTE_STREAMS] = {};
-    size_t       bytesA = 0, bytesB = 0, bytesC = 0, bytesW[COMPUTE_STREAMS] = {};
+    Slot         slot[SLOTS];
+    float*       ws[COMPUTE_STREAMS] = {}; // split-K workspaces, one per compute stream (stream order protects them)
+    size_t       bytesW[COMPUTE_STREAMS] = {};
     cudaStream_t up = nullptr, down = nullptr, compute[COMPUTE_STREAMS] = {};
-    cudaEvent_t  uploaded[MAX_STRIPS] = {};
-    cudaEvent_t  computed[MAX_STRIPS] = {};
+    long long    next_ticket = 0;
     int          sms = 0;
     bool         init = false;
 };
@@ -93,10 +106,6 @@ cudaError_t copy_block(float* dst, const float* src, int layout, size_t rows, si
 void cut(size_t dim, size_t* piece, int* count)
 {
     size_t want = std::min<size_t>(MAX_PIECES, std::max<size_t>(1, dim / 512));
-#ifdef B200_SGEMM_HOST_TRACE
-    if(const char* v = std::getenv("B200_HOST_PIECES"))
-        want = std::min<size_t>(MAX_PIECES, std::max<size_t>(1, std::atoi(v)));
-#endif
     size_t len  = (dim + want - 1) / want;
     len         = (len + 127) / 128 * 128;
     *piece      = len;
@@ -120,36 +129,65 @@ struct Strip
     size_t r0, rn, c0, cn;
     int    split;
 };
+struct Step
+{
+    bool  is_a;
+    int   piece;
+    bool  has_strip;
+    Strip strip;
+};
+
+cudaError_t init_ctx(HostCtx& x, int device)
+{
+    cudaError_t e;
+    if((e = cudaDeviceGetAttribute(&x.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return e;
+    if((e = cudaStreamCreateWithFlags(&x.up, cudaStreamNonBlocking)) != cudaSuccess) return e;
+    if((e = cudaStreamCreateWithFlags(&x.down, cudaStreamNonBlocking)) != cudaSuccess) return e;
+    for(int i = 0; i < COMPUTE_STREAMS; ++i)
+        if((e = cudaStreamCreateWithFlags(&x.compute[i], cudaStreamNonBlocking)) != cudaSuccess) return e;
+    for(Slot& s : x.slot)
+    {
+        for(int i = 0; i < MAX_STRIPS; ++i)
+        {
+            if((e = cudaEventCreateWithFlags(&s.uploaded[i], cudaEventDisableTiming)) != cudaSuccess) return e;
+            if((e = cudaEventCreateWithFlags(&s.computed[i], cudaEventDisableTiming)) != cudaSuccess) return e;
+        }
+        if((e = cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming)) != cudaSuccess) return e;
+    }
+    x.init = true;
+    return cudaSuccess;
+}
+
+// blocks until the job in this slot (if any) has finished
+cudaError_t drain(Slot& s)
+{
+    if(!s.busy)
+        return cudaSuccess;
+    cudaError_t e = cudaEventSynchronize(s.done);
+    s.busy        = false;
+    return e;
+}
 } // namespace
 
-extern "C" int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
-                               size_t M, size_t N, size_t K)
+extern "C" int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
+                                      size_t M, size_t N, size_t K, long long* ticket)
 {
-    if(!C || !A || !B || M == 0 || N == 0 || K == 0 || (layout_a | layout_b | layout_c) & ~1)
+    if(!C || !A || !B || !ticket || M == 0 || N == 0 || K == 0 || (layout_a | layout_b | layout_c) & ~1)
         return B200_SGEMM_INVALID_ARGUMENT;
     int         device = 0;
     cudaError_t e      = cudaGetDevice(&device);
     if(e != cudaSuccess)
         return (int)e;
-    std::lock_guard<std::mutex> lock(g_mutex); // one host-buffer call per process at a time: they share the arena
+    std::lock_guard<std::mutex> lock(g_mutex);
     HostCtx&                    x = g_ctx[device];
-    if(!x.init)
-    {
-        if((e = cudaDeviceGetAttribute(&x.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return (int)e;
-        if((e = cudaStreamCreateWithFlags(&x.up, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
-        if((e = cudaStreamCreateWithFlags(&x.down, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
-        for(int i = 0; i < COMPUTE_STREAMS; ++i)
-            if((e = cudaStreamCreateWithFlags(&x.compute[i], cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
-        for(int i = 0; i < MAX_STRIPS; ++i)
-        {
-            if((e = cudaEventCreateWithFlags(&x.uploaded[i], cudaEventDisableTiming)) != cudaSuccess) return (int)e;
-            if((e = cudaEventCreateWithFlags(&x.computed[i], cudaEventDisableTiming)) != cudaSuccess) return (int)e;
-        }
-        x.init = true;
-    }
+    if(!x.init && (e = init_ctx(x, device)) != cudaSuccess)
+        return (int)e;
+    Slot& sl = x.slot[x.next_ticket % SLOTS];
+    if((e = drain(sl)) != cudaSuccess) // the job submitted two calls ago owns this slot's device matrices
+        return (int)e;
 
     // Large problems: the table's kernel for big cubes, pieces and split-K chosen here.  Small ones: one
-    // piece per operand and whatever the table says for the shape.
+    // piece per operand and the table's kernel for the shape, unsplit.
     const bool big     = M >= 1024 && N >= 1024 && K >= 1024;
     int        variant = -1;
     size_t     pm = M, pn = N;
@@ -163,13 +201,6 @@ extern "C" int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* 
     }
 
     // the schedule: uploads in order, the strip each one makes computable
-    struct Step
-    {
-        bool  is_a;
-        int   piece;
-        bool  has_strip;
-        Strip strip;
-    };
     std::vector<Step> steps;
     size_t            rows_done = 0, cols_done = 0, ws_need = 0;
     for(int k = 0; k < std::max(nm, nn); ++k)
@@ -177,16 +208,14 @@ extern "C" int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* 
         if(k < nm)
         {
             const size_t r0 = size_t(k) * pm, rn = std::min(pm, M - r0);
-            Step         s{true, k, cols_done > 0, {r0, rn, 0, cols_done, 1}};
+            steps.push_back(Step{true, k, cols_done > 0, {r0, rn, 0, cols_done, 1}});
             rows_done = r0 + rn;
-            steps.push_back(s);
         }
         if(k < nn)
         {
             const size_t c0 = size_t(k) * pn, cn = std::min(pn, N - c0);
-            Step         s{false, k, rows_done > 0, {0, rows_done, c0, cn, 1}};
+            steps.push_back(Step{false, k, rows_done > 0, {0, rows_done, c0, cn, 1}});
             cols_done = c0 + cn;
-            steps.push_back(s);
         }
     }
     for(Step& s : steps)
@@ -198,100 +227,100 @@ extern "C" int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* 
                                                                      K, variant, s.strip.split));
     }
 
-    if((e = grow(&x.dA, &x.bytesA, M * K * sizeof(float))) != cudaSuccess) return (int)e;
-    if((e = grow(&x.dB, &x.bytesB, K * N * sizeof(float))) != cudaSuccess) return (int)e;
-    if((e = grow(&x.dC, &x.bytesC, M * N * sizeof(float))) != cudaSuccess) return (int)e;
-    for(int i = 0; i < COMPUTE_STREAMS; ++i)
-        if((e = grow(&x.ws[i], &x.bytesW[i], ws_need)) != cudaSuccess) return (int)e;
+    if((e = grow(&sl.dA, &sl.bytesA, M * K * sizeof(float))) != cudaSuccess) return (int)e;
+    if((e = grow(&sl.dB, &sl.bytesB, K * N * sizeof(float))) != cudaSuccess) return (int)e;
+    if((e = grow(&sl.dC, &sl.bytesC, M * N * sizeof(float))) != cudaSuccess) return (int)e;
+    if(ws_need > x.bytesW[0])
+    {
+        // a workspace may still be in use by the other slot's job: let it finish before the blocks are replaced
+        if((e = drain(x.slot[(x.next_ticket + 1) % SLOTS])) != cudaSuccess) return (int)e;
+        for(int i = 0; i < COMPUTE_STREAMS; ++i)
+            if((e = grow(&x.ws[i], &x.bytesW[i], ws_need)) != cudaSuccess) return (int)e;
+    }
 
     const size_t lda = layout_a == B200_SGEMM_ROW_MAJOR ? K : M;
     const size_t ldb = layout_b == B200_SGEMM_ROW_MAJOR ? N : K;
     const size_t ldc = layout_c == B200_SGEMM_ROW_MAJOR ? N : M;
     int          ev  = 0;
-#ifdef B200_SGEMM_HOST_TRACE
-    // timeline of one call: start/end of every upload, GEMM and download relative to the first upload
-    std::vector<cudaEvent_t> tev;
-    std::vector<const char*> tname;
-    auto mark = [&](cudaStream_t st, const char* name) {
-        cudaEvent_t q;
-        cudaEventCreate(&q);
-        cudaEventRecord(q, st);
-        tev.push_back(q);
-        tname.push_back(name);
-    };
-    mark(x.up, "start");
-#else
-    auto mark = [](cudaStream_t, const char*) {};
-#endif
     for(const Step& s : steps)
     {
         if(s.is_a)
         {
             const size_t r0 = size_t(s.piece) * pm, rn = std::min(pm, M - r0);
-            e = copy_block(x.dA, A, layout_a, M, K, r0, rn, 0, K, cudaMemcpyHostToDevice, x.up);
+            e = copy_block(sl.dA, A, layout_a, M, K, r0, rn, 0, K, cudaMemcpyHostToDevice, x.up);
         }
         else
         {
             const size_t c0 = size_t(s.piece) * pn, cn = std::min(pn, N - c0);
-            e = copy_block(x.dB, B, layout_b, K, N, 0, K, c0, cn, cudaMemcpyHostToDevice, x.up);
+            e = copy_block(sl.dB, B, layout_b, K, N, 0, K, c0, cn, cudaMemcpyHostToDevice, x.up);
         }
         if(e != cudaSuccess) return (int)e;
-        mark(x.up, s.is_a ? "A up end" : "B up end");
         if(!s.has_strip)
             continue; // the next upload's event also covers this one (same stream)
         const Strip& t = s.strip;
-        if((e = cudaEventRecord(x.uploaded[ev], x.up)) != cudaSuccess) return (int)e;
-        // strips rotate over several compute streams: the kernels are persistent (one CTA per SM, one or
-        // two tiles each), so the CTAs of the following strips start on the SMs that the last wave of the
-        // earlier ones leaves idle
+        if((e = cudaEventRecord(sl.uploaded[ev], x.up)) != cudaSuccess) return (int)e;
         const int    ci = ev % COMPUTE_STREAMS;
         cudaStream_t cs = x.compute[ci];
-        if((e = cudaStreamWaitEvent(cs, x.uploaded[ev], 0)) != cudaSuccess) return (int)e;
-        const float* ap = layout_a == B200_SGEMM_ROW_MAJOR ? x.dA + t.r0 * K : x.dA + t.r0;
-        const float* bp = layout_b == B200_SGEMM_ROW_MAJOR ? x.dB + t.c0 : x.dB + t.c0 * K;
-        float*       cp = layout_c == B200_SGEMM_ROW_MAJOR ? x.dC + t.r0 * N + t.c0 : x.dC + t.c0 * M + t.r0;
-        mark(cs, "gemm start");
+        if((e = cudaStreamWaitEvent(cs, sl.uploaded[ev], 0)) != cudaSuccess) return (int)e;
+        const float* ap = layout_a == B200_SGEMM_ROW_MAJOR ? sl.dA + t.r0 * K : sl.dA + t.r0;
+        const float* bp = layout_b == B200_SGEMM_ROW_MAJOR ? sl.dB + t.c0 : sl.dB + t.c0 * K;
+        float*       cp = layout_c == B200_SGEMM_ROW_MAJOR ? sl.dC + t.r0 * N + t.c0 : sl.dC + t.c0 * M + t.r0;
         const int    st = b200_sgemm_ex(layout_c, layout_a, layout_b, cp, ap, bp, t.rn, t.cn, K, lda, ldb, ldc, variant,
                                         t.split, x.ws[ci], x.bytesW[ci], cs);
-        mark(cs, "gemm end");
         if(st != B200_SGEMM_OK)
         {
             cudaDeviceSynchronize();
             return st;
         }
-        if((e = cudaEventRecord(x.computed[ev], cs)) != cudaSuccess) return (int)e;
-        if((e = cudaStreamWaitEvent(x.down, x.computed[ev], 0)) != cudaSuccess) return (int)e;
-        if((e = copy_block(C, x.dC, layout_c, M, N, t.r0, t.rn, t.c0, t.cn, cudaMemcpyDeviceToHost, x.down)) != cudaSuccess)
+        if((e = cudaEventRecord(sl.computed[ev], cs)) != cudaSuccess) return (int)e;
+        if((e = cudaStreamWaitEvent(x.down, sl.computed[ev], 0)) != cudaSuccess) return (int)e;
+        if((e = copy_block(C, sl.dC, layout_c, M, N, t.r0, t.rn, t.c0, t.cn, cudaMemcpyDeviceToHost, x.down)) != cudaSuccess)
             return (int)e;
-        mark(x.down, "down end");
         ++ev;
     }
-    if((e = cudaStreamSynchronize(x.down)) != cudaSuccess) return (int)e;
-    for(int i = 0; i < COMPUTE_STREAMS; ++i)
-        if((e = cudaStreamSynchronize(x.compute[i])) != cudaSuccess) return (int)e;
-    if((e = cudaStreamSynchronize(x.up)) != cudaSuccess) return (int)e;
-#ifdef B200_SGEMM_HOST_TRACE
-    if(std::getenv("B200_HOST_TRACE"))
-    {
-        int si = 0;
-        for(size_t i = 1; i < tev.size(); ++i)
-        {
-            float ms = 0;
-            cudaEventElapsedTime(&ms, tev[0], tev[i]);
-            std::printf("%8.3f ms  %s", ms, tname[i]);
-            if(tname[i][0] == 'g' && tname[i][5] == 's')
-            {
-                while(!steps[si].has_strip) ++si;
-                std::printf("  %zux%zu split %d", steps[si].strip.rn, steps[si].strip.cn, steps[si].strip.split);
-                ++si;
-            }
-            std::printf("\n");
-        }
-    }
-    for(cudaEvent_t q : tev)
-        cudaEventDestroy(q);
-#endif
+    // every download waits for its GEMM, every GEMM for its uploads: the end of the download stream is the end of the job
+    if((e = cudaEventRecord(sl.done, x.down)) != cudaSuccess) return (int)e;
+    sl.busy   = true;
+    sl.ticket = x.next_ticket;
+    *ticket   = x.next_ticket++;
     return B200_SGEMM_OK;
+}
+
+extern "C" int b200_sgemm_host_wait(long long ticket)
+{
+    int         device = 0;
+    cudaError_t e      = cudaGetDevice(&device);
+    if(e != cudaSuccess)
+        return (int)e;
+    cudaEvent_t done = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        auto                        it = g_ctx.find(device);
+        if(it == g_ctx.end() || ticket < 0 || ticket >= it->second.next_ticket)
+            return B200_SGEMM_INVALID_ARGUMENT;
+        Slot& sl = it->second.slot[ticket % SLOTS];
+        if(sl.ticket != ticket || !sl.busy)
+            return B200_SGEMM_OK; // already finished: its slot has been drained (and perhaps reused) since
+        done = sl.done;
+    }
+    e = cudaEventSynchronize(done); // outside the lock: other threads may submit meanwhile
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        Slot&                       sl = g_ctx[device].slot[ticket % SLOTS];
+        if(sl.ticket == ticket)
+            sl.busy = false;
+    }
+    return (int)e;
+}
+
+extern "C" int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
+                               size_t M, size_t N, size_t K)
+{
+    long long ticket = -1;
+    const int st     = b200_sgemm_host_submit(layout_c, layout_a, layout_b, C, A, B, M, N, K, &ticket);
+    if(st != B200_SGEMM_OK)
+        return st;
+    return b200_sgemm_host_wait(ticket);
 }
 
 extern "C" int b200_sgemm_shutdown_host(void)
@@ -303,9 +332,22 @@ extern "C" int b200_sgemm_shutdown_host(void)
     {
         HostCtx& x = kv.second;
         cudaSetDevice(kv.first);
-        cudaFree(x.dA);
-        cudaFree(x.dB);
-        cudaFree(x.dC);
+        for(Slot& s : x.slot)
+        {
+            drain(s);
+            cudaFree(s.dA);
+            cudaFree(s.dB);
+            cudaFree(s.dC);
+            if(x.init)
+            {
+                for(int i = 0; i < MAX_STRIPS; ++i)
+                {
+                    cudaEventDestroy(s.uploaded[i]);
+                    cudaEventDestroy(s.computed[i]);
+                }
+                cudaEventDestroy(s.done);
+            }
+        }
         for(int i = 0; i < COMPUTE_STREAMS; ++i)
             cudaFree(x.ws[i]);
         if(x.init)
@@ -314,11 +356,6 @@ extern "C" int b200_sgemm_shutdown_host(void)
             cudaStreamDestroy(x.down);
             for(int i = 0; i < COMPUTE_STREAMS; ++i)
                 cudaStreamDestroy(x.compute[i]);
-            for(int i = 0; i < MAX_STRIPS; ++i)
-            {
-                cudaEventDestroy(x.uploaded[i]);
-                cudaEventDestroy(x.computed[i]);
-            }
         }
     }
     g_ctx.clear();

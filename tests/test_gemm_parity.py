@@ -371,3 +371,28 @@ def test_host_buffer_entry_strips(sgemm, orc, layout):
     # every strip is an ordered split-K sum of FMA chains: the plain chain is within a few ulp of it
     want = orc.sgemm_fma(lc, la, lb, A, B, M, N, K, threads=orc.max_threads())
     assert np.max(np.abs(hC.numpy() - want)) <= 1e-4
+
+
+def test_host_buffer_submit_wait(sgemm, orc):
+    """Asynchronous form of the host-buffer entry: several jobs submitted back to back (two in flight, the third
+    submit waits for the first), tickets awaited in and out of order, every result bit-exact."""
+    la, lb, lc = 0, 0, 0
+    shapes = [(1100, 1536, 1024), (300, 200, 64), (2304, 1280, 1280), (130, 70, 33), (1024, 1024, 1024)]
+    jobs = []
+    for i, (M, N, K) in enumerate(shapes):
+        A, B = orc.fill_ab(70 + i, la, lb, M, N, K)
+        hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+        hC = torch.full((M * N,), float("nan"), dtype=torch.float32).pin_memory()
+        t = sgemm.gemm_host_submit(lc, la, lb, hC, hA, hB, M, N, K)
+        jobs.append((t, (M, N, K), A, B, hA, hB, hC))
+    assert [j[0] for j in jobs] == list(range(jobs[0][0], jobs[0][0] + len(jobs)))
+    for j in (jobs[3], jobs[4], jobs[0], jobs[2], jobs[1]):  # any order; finished tickets return at once
+        sgemm.gemm_host_wait(j[0])
+    sgemm.gemm_host_wait(jobs[0][0])  # waiting twice is harmless
+    for t, (M, N, K), A, B, hA, hB, hC in jobs:
+        full_check_f64_on_device(la, lb, lc, A, B, M, N, K, hC.numpy(), 1e-5 * math.sqrt(K))
+        if M < 1024:  # small problems run unsplit: bit-exact against the plain chain
+            want = orc.sgemm_fma(lc, la, lb, A, B, M, N, K, threads=orc.max_threads())
+            assert np.array_equal(bits(hC.numpy()), bits(want))
+    with pytest.raises(sgemm.SgemmError):
+        sgemm.gemm_host_wait(jobs[-1][0] + 1000)  # never issued
