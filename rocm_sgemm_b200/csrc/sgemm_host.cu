@@ -241,45 +241,51 @@ extern "C" int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, 
     const size_t lda = layout_a == B200_SGEMM_ROW_MAJOR ? K : M;
     const size_t ldb = layout_b == B200_SGEMM_ROW_MAJOR ? N : K;
     const size_t ldc = layout_c == B200_SGEMM_ROW_MAJOR ? N : M;
-    int          ev  = 0;
-    for(const Step& s : steps)
+    auto enqueue = [&]() -> int {
+        int ev = 0;
+        for(const Step& s : steps)
+        {
+            if(s.is_a)
+            {
+                const size_t r0 = size_t(s.piece) * pm, rn = std::min(pm, M - r0);
+                e = copy_block(sl.dA, A, layout_a, M, K, r0, rn, 0, K, cudaMemcpyHostToDevice, x.up);
+            }
+            else
+            {
+                const size_t c0 = size_t(s.piece) * pn, cn = std::min(pn, N - c0);
+                e = copy_block(sl.dB, B, layout_b, K, N, 0, K, c0, cn, cudaMemcpyHostToDevice, x.up);
+            }
+            if(e != cudaSuccess) return (int)e;
+            if(!s.has_strip)
+                continue; // the next upload's event also covers this one (same stream)
+            const Strip& t = s.strip;
+            if((e = cudaEventRecord(sl.uploaded[ev], x.up)) != cudaSuccess) return (int)e;
+            const int    ci = ev % COMPUTE_STREAMS;
+            cudaStream_t cs = x.compute[ci];
+            if((e = cudaStreamWaitEvent(cs, sl.uploaded[ev], 0)) != cudaSuccess) return (int)e;
+            const float* ap = layout_a == B200_SGEMM_ROW_MAJOR ? sl.dA + t.r0 * K : sl.dA + t.r0;
+            const float* bp = layout_b == B200_SGEMM_ROW_MAJOR ? sl.dB + t.c0 : sl.dB + t.c0 * K;
+            float*       cp = layout_c == B200_SGEMM_ROW_MAJOR ? sl.dC + t.r0 * N + t.c0 : sl.dC + t.c0 * M + t.r0;
+            const int    st = b200_sgemm_ex(layout_c, layout_a, layout_b, cp, ap, bp, t.rn, t.cn, K, lda, ldb, ldc, variant,
+                                            t.split, x.ws[ci], x.bytesW[ci], cs);
+            if(st != B200_SGEMM_OK)
+                return st;
+            if((e = cudaEventRecord(sl.computed[ev], cs)) != cudaSuccess) return (int)e;
+            if((e = cudaStreamWaitEvent(x.down, sl.computed[ev], 0)) != cudaSuccess) return (int)e;
+            if((e = copy_block(C, sl.dC, layout_c, M, N, t.r0, t.rn, t.c0, t.cn, cudaMemcpyDeviceToHost, x.down)) != cudaSuccess)
+                return (int)e;
+            ++ev;
+        }
+        // every download waits for its GEMM, every GEMM for its uploads: the end of the download stream is the end of the job
+        if((e = cudaEventRecord(sl.done, x.down)) != cudaSuccess) return (int)e;
+        return B200_SGEMM_OK;
+    };
+    const int status = enqueue();
+    if(status != B200_SGEMM_OK)
     {
-        if(s.is_a)
-        {
-            const size_t r0 = size_t(s.piece) * pm, rn = std::min(pm, M - r0);
-            e = copy_block(sl.dA, A, layout_a, M, K, r0, rn, 0, K, cudaMemcpyHostToDevice, x.up);
-        }
-        else
-        {
-            const size_t c0 = size_t(s.piece) * pn, cn = std::min(pn, N - c0);
-            e = copy_block(sl.dB, B, layout_b, K, N, 0, K, c0, cn, cudaMemcpyHostToDevice, x.up);
-        }
-        if(e != cudaSuccess) return (int)e;
-        if(!s.has_strip)
-            continue; // the next upload's event also covers this one (same stream)
-        const Strip& t = s.strip;
-        if((e = cudaEventRecord(sl.uploaded[ev], x.up)) != cudaSuccess) return (int)e;
-        const int    ci = ev % COMPUTE_STREAMS;
-        cudaStream_t cs = x.compute[ci];
-        if((e = cudaStreamWaitEvent(cs, sl.uploaded[ev], 0)) != cudaSuccess) return (int)e;
-        const float* ap = layout_a == B200_SGEMM_ROW_MAJOR ? sl.dA + t.r0 * K : sl.dA + t.r0;
-        const float* bp = layout_b == B200_SGEMM_ROW_MAJOR ? sl.dB + t.c0 : sl.dB + t.c0 * K;
-        float*       cp = layout_c == B200_SGEMM_ROW_MAJOR ? sl.dC + t.r0 * N + t.c0 : sl.dC + t.c0 * M + t.r0;
-        const int    st = b200_sgemm_ex(layout_c, layout_a, layout_b, cp, ap, bp, t.rn, t.cn, K, lda, ldb, ldc, variant,
-                                        t.split, x.ws[ci], x.bytesW[ci], cs);
-        if(st != B200_SGEMM_OK)
-        {
-            cudaDeviceSynchronize();
-            return st;
-        }
-        if((e = cudaEventRecord(sl.computed[ev], cs)) != cudaSuccess) return (int)e;
-        if((e = cudaStreamWaitEvent(x.down, sl.computed[ev], 0)) != cudaSuccess) return (int)e;
-        if((e = copy_block(C, sl.dC, layout_c, M, N, t.r0, t.rn, t.c0, t.cn, cudaMemcpyDeviceToHost, x.down)) != cudaSuccess)
-            return (int)e;
-        ++ev;
+        cudaDeviceSynchronize(); // whatever was enqueued before the failure must not outlive the slot's reuse
+        return status;
     }
-    // every download waits for its GEMM, every GEMM for its uploads: the end of the download stream is the end of the job
-    if((e = cudaEventRecord(sl.done, x.down)) != cudaSuccess) return (int)e;
     sl.busy   = true;
     sl.ticket = x.next_ticket;
     *ticket   = x.next_ticket++;

@@ -95,6 +95,34 @@ bool verify_gemm(int la, int lb, int lc, size_t M, size_t N, size_t K, cudaStrea
             }
     return true;
 }
+// The vendor-wrapper signature served by this library (rocm_sgemm::blas::gemm<TA, TB>): column-major C, the
+// transpose flags select how A and B are stored; what the reference's test/rocblas/test.cpp checks for its wrapper.
+template<bool TA, bool TB>
+bool verify_blas(size_t M, size_t N, size_t K, cudaStream_t stream)
+{
+    // op(A) = A^T means A is stored K x M column-major, i.e. the M x K operand is row-major
+    const layout la = TA ? layout::row_major : layout::col_major, lb = TB ? layout::row_major : layout::col_major;
+    host_matrix hA(M, K, la), hB(K, N, lb), hC(M, N, layout::col_major), hRef(M, N, layout::col_major);
+    fill_like_reference_test(hA);
+    fill_like_reference_test(hB);
+    device_buffers d(hA.bytes(), hB.bytes(), hC.bytes());
+    CUDA_CHECK(cudaMemcpy(d.A, hA.data(), hA.bytes(), cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemcpy(d.B, hB.data(), hB.bytes(), cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemset(d.C, 0xff, hC.bytes()));
+    rocm_sgemm::blas::gemm<TA, TB>(d.C, d.A, d.B, M, N, K, stream);
+    CUDA_CHECK(cudaPeekAtLastError());
+    CUDA_CHECK(cudaDeviceSynchronize());
+    CUDA_CHECK(cudaMemcpy(hC.data(), d.C, hC.bytes(), cudaMemcpyDeviceToHost));
+    host_sgemm(hRef, hA, hB, 0, M);
+    for(size_t i = 0; i < M; ++i)
+        for(size_t j = 0; j < N; ++j)
+            if(!(std::fabs(hC(i, j) - hRef(i, j)) <= 1e-4f))
+            {
+                std::printf("    mismatch at (%zu,%zu): %.9g vs %.9g\n", i, j, hC(i, j), hRef(i, j));
+                return false;
+            }
+    return true;
+}
 } // namespace
 
 int main()
@@ -123,6 +151,19 @@ int main()
                 std::printf("[%s] GEMMTest/%s%s%s.IdentityBitExact512\n", ok ? "  OK  " : "FAILED", layout_letter((layout)la),
                             layout_letter((layout)lb), layout_letter((layout)lc));
             }
+    const size_t blas_shapes[][3] = {{128, 128, 128}, {320, 512, 512}, {130, 70, 33}, {1024, 256, 256}};
+    for(const auto& s : blas_shapes)
+    {
+        const bool ok[4] = {verify_blas<false, false>(s[0], s[1], s[2], stream), verify_blas<true, false>(s[0], s[1], s[2], stream),
+                            verify_blas<false, true>(s[0], s[1], s[2], stream), verify_blas<true, true>(s[0], s[1], s[2], stream)};
+        const char* names[4] = {"NN", "TN", "NT", "TT"};
+        for(int i = 0; i < 4; ++i)
+        {
+            ++run;
+            failed += !ok[i];
+            std::printf("[%s] BlasWrapperTest/%s.Size%zux%zux%zu\n", ok[i] ? "  OK  " : "FAILED", names[i], s[0], s[1], s[2]);
+        }
+    }
     CUDA_CHECK(cudaStreamDestroy(stream));
     std::printf("%d tests, %d failed\n", run, failed);
     return failed == 0 ? 0 : 1;
