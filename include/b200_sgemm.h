@@ -156,6 +156,11 @@ int b200_sgemm_host(int layout_c, int layout_a, int layout_b, float* C, const fl
 int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
                            size_t N, size_t K, long long* ticket);
 int b200_sgemm_host_wait(long long ticket);
+/* The schedule the host-buffer entries use for an M x N x K problem on a device with sm_count SMs, without touching a
+ * device: returns the number of strips of C (one GEMM each, in launch order) and writes the first `capacity` of them
+ * as (first row, rows, first column, columns) into rects[4*i..] and their split-K factors into splits[i].  The
+ * strips tile C exactly once.  Negative return = B200_SGEMM_INVALID_ARGUMENT. */
+int b200_sgemm_host_plan(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits, int capacity);
 int b200_sgemm_shutdown_host(void);
 
 /* The same product for `batch` matrices at fixed element strides: matrix b uses C + b*stride_c, A + b*stride_a,

@@ -137,6 +137,48 @@ struct Step
     Strip strip;
 };
 
+// The schedule of one job: the uploads in order (row panels of A and column panels of B alternately) and, for each,
+// the rectangle of C it makes computable.  Pure host arithmetic (exported for tests as b200_sgemm_host_plan).
+struct Plan
+{
+    bool              big = false; // large problem: pieces, the big-cube kernel and split-K chosen here
+    size_t            pm = 0, pn = 0;
+    std::vector<Step> steps;
+};
+Plan make_plan(size_t M, size_t N, size_t K, int sms)
+{
+    Plan p;
+    p.big = M >= 1024 && N >= 1024 && K >= 1024;
+    p.pm  = M;
+    p.pn  = N;
+    int nm = 1, nn = 1;
+    if(p.big)
+    {
+        cut(M, &p.pm, &nm);
+        cut(N, &p.pn, &nn);
+    }
+    size_t rows_done = 0, cols_done = 0;
+    for(int k = 0; k < std::max(nm, nn); ++k)
+    {
+        if(k < nm)
+        {
+            const size_t r0 = size_t(k) * p.pm, rn = std::min(p.pm, M - r0);
+            p.steps.push_back(Step{true, k, cols_done > 0, {r0, rn, 0, cols_done, 1}});
+            rows_done = r0 + rn;
+        }
+        if(k < nn)
+        {
+            const size_t c0 = size_t(k) * p.pn, cn = std::min(p.pn, N - c0);
+            p.steps.push_back(Step{false, k, rows_done > 0, {0, rows_done, c0, cn, 1}});
+            cols_done = c0 + cn;
+        }
+    }
+    for(Step& s : p.steps)
+        if(s.has_strip)
+            s.strip.split = p.big ? pick_split(s.strip.rn, s.strip.cn, K, sms) : 1;
+    return p;
+}
+
 cudaError_t init_ctx(HostCtx& x, int device)
 {
     cudaError_t e;
@@ -186,46 +228,19 @@ extern "C" int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, 
     if((e = drain(sl)) != cudaSuccess) // the job submitted two calls ago owns this slot's device matrices
         return (int)e;
 
-    // Large problems: the table's kernel for big cubes, pieces and split-K chosen here.  Small ones: one
-    // piece per operand and the table's kernel for the shape, unsplit.
-    const bool big     = M >= 1024 && N >= 1024 && K >= 1024;
-    int        variant = -1;
-    size_t     pm = M, pn = N;
-    int        nm = 1, nn = 1;
-    if(big)
-    {
-        if(b200_sgemm_select_config(layout_c, layout_a, layout_b, 4096, 4096, 4096, nullptr, &variant) != B200_SGEMM_OK)
-            variant = -1;
-        cut(M, &pm, &nm);
-        cut(N, &pn, &nn);
-    }
-
-    // the schedule: uploads in order, the strip each one makes computable
-    std::vector<Step> steps;
-    size_t            rows_done = 0, cols_done = 0, ws_need = 0;
-    for(int k = 0; k < std::max(nm, nn); ++k)
-    {
-        if(k < nm)
-        {
-            const size_t r0 = size_t(k) * pm, rn = std::min(pm, M - r0);
-            steps.push_back(Step{true, k, cols_done > 0, {r0, rn, 0, cols_done, 1}});
-            rows_done = r0 + rn;
-        }
-        if(k < nn)
-        {
-            const size_t c0 = size_t(k) * pn, cn = std::min(pn, N - c0);
-            steps.push_back(Step{false, k, rows_done > 0, {0, rows_done, c0, cn, 1}});
-            cols_done = c0 + cn;
-        }
-    }
-    for(Step& s : steps)
-    {
-        if(!s.has_strip)
-            continue;
-        s.strip.split = big ? pick_split(s.strip.rn, s.strip.cn, K, x.sms) : 1;
-        ws_need       = std::max(ws_need, b200_sgemm_workspace_bytes(layout_c, layout_a, layout_b, s.strip.rn, s.strip.cn,
-                                                                     K, variant, s.strip.split));
-    }
+    // Large problems run the table's kernel for big cubes on every strip; small ones (one piece per operand) the
+    // table's kernel for their shape, unsplit.
+    Plan                     plan  = make_plan(M, N, K, x.sms);
+    const std::vector<Step>& steps = plan.steps;
+    const size_t             pm = plan.pm, pn = plan.pn;
+    int                      variant = -1;
+    if(plan.big && b200_sgemm_select_config(layout_c, layout_a, layout_b, 4096, 4096, 4096, nullptr, &variant) != B200_SGEMM_OK)
+        variant = -1;
+    size_t ws_need = 0;
+    for(const Step& s : steps)
+        if(s.has_strip)
+            ws_need = std::max(ws_need, b200_sgemm_workspace_bytes(layout_c, layout_a, layout_b, s.strip.rn, s.strip.cn, K,
+                                                                   variant, s.strip.split));
 
     if((e = grow(&sl.dA, &sl.bytesA, M * K * sizeof(float))) != cudaSuccess) return (int)e;
     if((e = grow(&sl.dB, &sl.bytesB, K * N * sizeof(float))) != cudaSuccess) return (int)e;
@@ -290,6 +305,29 @@ extern "C" int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, 
     sl.ticket = x.next_ticket;
     *ticket   = x.next_ticket++;
     return B200_SGEMM_OK;
+}
+
+extern "C" int b200_sgemm_host_plan(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits, int capacity)
+{
+    if(M == 0 || N == 0 || K == 0 || sm_count < 1 || capacity < 0 || (capacity > 0 && (!rects || !splits)))
+        return B200_SGEMM_INVALID_ARGUMENT;
+    const Plan p = make_plan(M, N, K, sm_count);
+    int        n = 0;
+    for(const Step& s : p.steps)
+    {
+        if(!s.has_strip)
+            continue;
+        if(n < capacity)
+        {
+            rects[4 * n + 0] = s.strip.r0;
+            rects[4 * n + 1] = s.strip.rn;
+            rects[4 * n + 2] = s.strip.c0;
+            rects[4 * n + 3] = s.strip.cn;
+            splits[n]        = s.strip.split;
+        }
+        ++n;
+    }
+    return n;
 }
 
 extern "C" int b200_sgemm_host_wait(long long ticket)
