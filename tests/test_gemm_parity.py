@@ -396,3 +396,39 @@ def test_host_buffer_submit_wait(sgemm, orc):
             assert np.array_equal(bits(hC.numpy()), bits(want))
     with pytest.raises(sgemm.SgemmError):
         sgemm.gemm_host_wait(jobs[-1][0] + 1000)  # never issued
+
+
+def test_reentrant_threads_and_streams(sgemm, orc):
+    """Four host threads, each with its own stream, call the drop-in entry concurrently (split-K and pre-transposing
+    table entries included, so the per-(device, stream) arenas are in play); every result stays bit-exact."""
+    import threading
+    cases = [((1024, 1024, 1024), (0, 1, 0)), ((1027, 1030, 37), (1, 0, 1)), ((2048, 2048, 2048), (0, 0, 0)),
+             ((300, 200, 4096), (1, 1, 0))]
+    inputs = []
+    for i, ((M, N, K), (la, lb, lc)) in enumerate(cases):
+        A, B = orc.fill_ab(80 + i, la, lb, M, N, K)
+        inputs.append((dev(A), dev(B), torch.full((M * N,), float("nan"), device="cuda"), A, B))
+    errors = []
+
+    def work(i):
+        try:
+            (M, N, K), (la, lb, lc) = cases[i]
+            dA, dB, dC, _, _ = inputs[i]
+            s = torch.cuda.Stream()
+            for _ in range(6):
+                sgemm.gemm(lc, la, lb, dC, dA, dB, M, N, K, stream=s)
+            s.synchronize()
+        except Exception as ex:  # surfaced in the main thread below
+            errors.append((i, repr(ex)))
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(cases))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    torch.cuda.synchronize()
+    for i, ((M, N, K), (la, lb, lc)) in enumerate(cases):
+        _, _, dC, A, B = inputs[i]
+        expect_bit_exact(sgemm, orc, la, lb, lc, A, B, M, N, K, dC.cpu().numpy())
+    assert sgemm.device_status() == 0
