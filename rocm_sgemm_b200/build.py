@@ -99,7 +99,7 @@ def build_library(config: Path | None = None, jobs: int | None = None, verbose=F
     generate(config, extra_pairs)
     sources = [GEN / s for s in (GEN / "sources.txt").read_text().split()]
     kernel_hdr = [CSRC / "sgemm_kernel.cuh", CSRC / "sgemm_ws_kernel.cuh"]
-    api_deps = kernel_hdr + [CSRC / "config_select.hpp", GEN / "config_table.inc", REPO / "include" / "b200_sgemm.h"]
+    api_deps = kernel_hdr + [CSRC / "transpose.hpp", CSRC / "config_select.hpp", GEN / "config_table.inc", REPO / "include" / "b200_sgemm.h"]
     jobs = jobs or max(1, (os.cpu_count() or 2))
     BUILD.mkdir(exist_ok=True)
     ptxas_log = BUILD / "ptxas.log"
@@ -107,7 +107,7 @@ def build_library(config: Path | None = None, jobs: int | None = None, verbose=F
     work.append((CSRC / "sgemm_api.cu", api_deps))
     work.append((CSRC / "sgemm_static_scratch.cu", [REPO / "include" / "b200_sgemm.h"]))
     work.append((CSRC / "sgemm_host.cu", [REPO / "include" / "b200_sgemm.h"]))
-    work.append((CSRC / "sgemm_tf32x3.cu", kernel_hdr + [REPO / "include" / "b200_sgemm.h"]))
+    work.append((CSRC / "sgemm_tf32x3.cu", kernel_hdr + [CSRC / "transpose.hpp", REPO / "include" / "b200_sgemm.h"]))
     work.append((CSRC / "sgemm_blas.cu", [REPO / "include" / "b200_sgemm.h"]))
     objs = []
     with cf.ThreadPoolExecutor(max_workers=jobs) as ex:

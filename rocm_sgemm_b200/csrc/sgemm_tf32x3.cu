@@ -28,6 +28,7 @@
 // Every mbarrier wait is bounded; on a time-out the CTA records a status word, stops and frees its TMEM.
 #include "../../include/b200_sgemm.h"
 #include "sgemm_ws_kernel.cuh"
+#include "transpose.hpp"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -431,35 +432,19 @@ __global__ void __launch_bounds__(T_THREADS, 1)
 }
 
 // ---- repacking of operands that the kernel cannot read in place ------------------------------------------
-// dst is R rows of Kp floats (K-contiguous, zero padded from K to Kp).  src is the packed R x K operand,
-// either K-contiguous (src[r*K + k]) or R-contiguous (src[k*R + r]).
+// A K-contiguous operand whose pitch is not a multiple of 16 bytes (K % 4 != 0) or whose base is misaligned is copied
+// into R rows of Kp floats (zero padded from K to Kp).  Operands that are not K-contiguous go through the library's
+// transposition (launch_transpose) instead.
 __global__ void __launch_bounds__(256) repack_kernel(float* __restrict__ dst, const float* __restrict__ src, int R, int K,
-                                                     int Kp, int src_k_contiguous)
+                                                     int Kp)
 {
-    __shared__ float tile[32][33];
     const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
-    if(src_k_contiguous)
-    {
-        for(int i = ty; i < 32; i += 8)
-        {
-            const int r = r0 + i, k = k0 + tx;
-            if(r < R && k < Kp)
-                dst[size_t(r) * Kp + k] = k < K ? src[size_t(r) * K + k] : 0.f;
-        }
-        return;
-    }
-    for(int i = ty; i < 32; i += 8)
-    {
-        const int k = k0 + i, r = r0 + tx;
-        tile[i][tx] = (k < K && r < R) ? src[size_t(k) * R + r] : 0.f;
-    }
-    __syncthreads();
     for(int i = ty; i < 32; i += 8)
     {
         const int r = r0 + i, k = k0 + tx;
         if(r < R && k < Kp)
-            dst[size_t(r) * Kp + k] = tile[tx][i];
+            dst[size_t(r) * Kp + k] = k < K ? src[size_t(r) * K + k] : 0.f;
     }
 }
 
@@ -572,15 +557,25 @@ extern "C" int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float
     if(!a_direct)
     {
         if((e = grow(&s.a, &s.bytes_a, M * Kp * sizeof(float))) != cudaSuccess) return (int)e;
-        dim3 grid((unsigned)((Kp + 31) / 32), (unsigned)((M + 31) / 32));
-        repack_kernel<<<grid, 256, 0, stream>>>(s.a, A, (int)M, (int)K, (int)Kp, layout_a == B200_SGEMM_ROW_MAJOR);
+        if(layout_a == B200_SGEMM_ROW_MAJOR) // K-contiguous already: copy with the padded pitch
+        {
+            dim3 grid((unsigned)((Kp + 31) / 32), (unsigned)((M + 31) / 32));
+            repack_kernel<<<grid, 256, 0, stream>>>(s.a, A, (int)M, (int)K, (int)Kp);
+        }
+        else // col-major A = K rows of M contiguous floats -> M rows of K (the pad columns are never read)
+            launch_transpose(A, s.a, K, M, M, Kp, stream);
         a_src = s.a;
     }
     if(!b_direct)
     {
         if((e = grow(&s.b, &s.bytes_b, N * Kp * sizeof(float))) != cudaSuccess) return (int)e;
-        dim3 grid((unsigned)((Kp + 31) / 32), (unsigned)((N + 31) / 32));
-        repack_kernel<<<grid, 256, 0, stream>>>(s.b, B, (int)N, (int)K, (int)Kp, layout_b == B200_SGEMM_COL_MAJOR);
+        if(layout_b == B200_SGEMM_COL_MAJOR)
+        {
+            dim3 grid((unsigned)((Kp + 31) / 32), (unsigned)((N + 31) / 32));
+            repack_kernel<<<grid, 256, 0, stream>>>(s.b, B, (int)N, (int)K, (int)Kp);
+        }
+        else // row-major B = K rows of N contiguous floats -> N rows of K
+            launch_transpose(B, s.b, K, N, N, Kp, stream);
         b_src = s.b;
     }
     if((e = cudaPeekAtLastError()) != cudaSuccess)
