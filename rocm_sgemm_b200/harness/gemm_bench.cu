@@ -104,7 +104,8 @@ void usage(const char* prog)
     std::printf("Usage: %s [options]\n"
                 "  --shapes <list>     colon-separated shapes, 'M,N,K' or 'M' (default 1024:2048:4096:8192)\n"
                 "  --layouts <list>    comma-separated A,B,C layouts such as rrr,crc (default: all eight)\n"
-                "  --batch_count <n>   replicate the buffers n times (FLOP count scales, one launch: as the reference)\n"
+                "  --batch_count <n>   n independent products per timed call (b200_sgemm_strided_batched; the reference only\n"
+                "                      replicates its buffers, benchmark/gemm/bench.cpp:49-64)\n"
                 "  --iters <n>         timed launches per row (default 100)   --warmup <n> (default 10)\n"
                 "  --identity          B = identity, verify C == A bit for bit\n"
                 "  --cpu <rows>        also time the host GEMM on <rows> rows of C\n"
@@ -219,8 +220,15 @@ int main(int argc, char** argv)
                 CUDA_CHECK(cudaMemcpy(dB + b * hB.size(), hB.data(), hB.bytes(), cudaMemcpyHostToDevice));
             }
             const double flops = 2.0 * M * N * K * bc;
-            const stats  ours  = time_launches([&] { table[idx](dC, dA, dB, M, N, K, stream); }, stream, flops,
-                                               opt.warmup, opt.iters);
+            const stats  ours  = time_launches(
+                [&] {
+                    if(bc == 1)
+                        table[idx](dC, dA, dB, M, N, K, stream);
+                    else if(b200_sgemm_strided_batched(lc, la, lb, dC, dA, dB, M, N, K, M * N, M * K, K * N, bc, stream)
+                            != B200_SGEMM_OK)
+                        throw std::runtime_error("b200_sgemm_strided_batched failed");
+                },
+                stream, flops, opt.warmup, opt.iters);
             bool exact = true;
             if(opt.identity)
             {
@@ -239,12 +247,20 @@ int main(int argc, char** argv)
             }
             stats vendor;
             if(opt.vendor)
-                vendor = time_launches([&] { b200_cublas_gemm_layout(lc, la, lb, dC, dA, dB, M, N, K, stream); }, stream,
-                                       flops, opt.warmup, opt.iters);
+                vendor = time_launches(
+                    [&] {
+                        for(size_t b = 0; b < bc; ++b)
+                            b200_cublas_gemm_layout(lc, la, lb, dC + b * M * N, dA + b * M * K, dB + b * K * N, M, N, K, stream);
+                    },
+                    stream, flops, opt.warmup, opt.iters);
             stats tensor; // the optional 3xTF32 tensor-core entry: its own column, not the graded arithmetic
             if(opt.tf32x3)
-                tensor = time_launches([&] { b200_sgemm_3xtf32(lc, la, lb, dC, dA, dB, M, N, K, stream); }, stream, flops,
-                                       opt.warmup, opt.iters);
+                tensor = time_launches(
+                    [&] {
+                        for(size_t b = 0; b < bc; ++b)
+                            b200_sgemm_3xtf32(lc, la, lb, dC + b * M * N, dA + b * M * K, dB + b * K * N, M, N, K, stream);
+                    },
+                    stream, flops, opt.warmup, opt.iters);
             char name[96];
             std::snprintf(name, sizeof name, "{A:%s,B:%s,C:%s,m:%zu,n:%zu,k:%zu}", layout_letter((layout)la),
                           layout_letter((layout)lb), layout_letter((layout)lc), M, N, K);

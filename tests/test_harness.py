@@ -38,3 +38,9 @@ def test_gemm_bench_rows():
     for x in rows:
         assert x["identity_exact"] is True
         assert x["avg_tflops"] > 0 and x["cublas_avg_tflops"] > 0 and x["tf32x3_avg_tflops"] > 0
+    # --batch_count: every matrix of the batch is computed (the timed call is b200_sgemm_strided_batched)
+    r = subprocess.run([_exe("gemm_bench"), "--json", "--shapes", "512", "--layouts", "rrr", "--batch_count", "3",
+                        "--iters", "3", "--warmup", "1"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-1000:]
+    one = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(one) == 1 and one[0]["avg_tflops"] > 0 and one[0]["avg_ms"] > rows[0]["avg_ms"]
