@@ -361,9 +361,28 @@ def ours(args, w):
 
     hC2_t = torch.empty(M * Nl, dtype=torch.float32).pin_memory()
 
+    # what this box's PCIe link gives a plain pinned copy (explains the end-to-end figure: the uploads bound it)
+    def copy_gbs(dst, src):
+        n = min(dst.numel(), src.numel(), 16 * 1024 * 1024)  # 64 MiB
+        for _ in range(2):
+            dst[:n].copy_(src[:n], non_blocking=True)
+        torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(4):
+            dst[:n].copy_(src[:n], non_blocking=True)
+        c1.record()
+        c1.synchronize()
+        return 4 * n * 4 / (c0.elapsed_time(c1) * 1e-3) / 1e9
+
+    pcie_h2d_gbs = copy_gbs(dA, hA_t)
+    pcie_d2h_gbs = copy_gbs(hC_t, dC)
+
     def e2e_step():
         # one blocking call of the C ABI with HOST buffers: upload, GEMM and download overlapped inside the library
         sg.gemm_host(lc, la, lb, hC_t, hA_t, hB_t, M, Nl, K)
+
+    submit_cpu_ms = []  # host time spent inside submit (it includes waiting for the slot of the job two steps back)
 
     def e2e_stream(steps):
         # the same call split into submit / wait, two jobs in flight: step i+1 is submitted before the result of
@@ -371,7 +390,9 @@ def ours(args, w):
         # step uploads its A and B from pinned host memory and downloads its C (alternating host buffers).
         pending = []
         for i in range(steps):
+            t0 = time.perf_counter()
             pending.append(sg.gemm_host_submit(lc, la, lb, hC_t if i % 2 == 0 else hC2_t, hA_t, hB_t, M, Nl, K))
+            submit_cpu_ms.append((time.perf_counter() - t0) * 1e3)
             if len(pending) > 1:
                 sg.gemm_host_wait(pending.pop(0))
         for t in pending:
@@ -403,7 +424,10 @@ def ours(args, w):
            "steps": e2e_steps, "h2d_bytes_per_step": (hA_t.numel() + hB_t.numel()) * 4 * G,
            "d2h_bytes_per_step": hC_t.numel() * 4 * G,
            "mode": "b200_sgemm_host_submit / _wait, two steps in flight (every step uploads A, B and downloads C)",
-           "blocking_call_ms": blocking_ms, "blocking_call_tflops": flops_total / (blocking_ms * 1e-3) / 1e12}
+           "blocking_call_ms": blocking_ms, "blocking_call_tflops": flops_total / (blocking_ms * 1e-3) / 1e12,
+           "submit_cpu_ms_median": statistics.median(submit_cpu_ms[-e2e_steps:]),
+           "pcie_h2d_gbs": pcie_h2d_gbs, "pcie_d2h_gbs": pcie_d2h_gbs,
+           "upload_bound_ms": (hA_t.numel() + hB_t.numel()) * 4 / (pcie_h2d_gbs * 1e9) * 1e3}
 
     if rank != 0:
         if world > 1:
