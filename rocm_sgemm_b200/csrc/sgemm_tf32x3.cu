@@ -4,7 +4,8 @@
 // is an FP32 FMA chain) and has no counterpart in the reference; it exists as a comparison column
 // showing what the same FP32 problem costs when a relative error of about 2e-6 is acceptable.
 //
-//   a = a_hi + a_lo,  a_hi = tf32(a),  a_lo = tf32(a - a_hi)          (both round-to-nearest)
+//   a = a_hi + a_lo,  a_hi = a with its low 13 mantissa bits dropped (what the tensor core reads from the raw
+//   word),  a_lo = the exact remainder a - a_hi rounded to nearest TF32
 //   A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi                          (three tensor-core products)
 //
 // Kernel: one persistent CTA per SM (16 warps), 128 x 256 tiles, K blocks of 16 floats (= one 64-byte swizzle row),
