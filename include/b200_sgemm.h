@@ -197,17 +197,20 @@ int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float* C, const 
 int b200_sgemm_3xtf32_device_status(void);
 int b200_sgemm_3xtf32_shutdown(void);
 
-/* Size of the scratch array that b200_sgemm_splitk_static uses; it is part of the library image. */
+/* Size of the scratch array that b200_sgemm_splitk_static uses; it is part of the library's device image. */
 #define B200_SGEMM_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 
 /* Split-K GEMM for callers that cannot allocate device memory and cannot pass a workspace: hosts whose
  * memory pool already owns the whole device, latency-bound threads that must stay out of the driver's
  * allocator, plug-ins barred from allocating after their init hook.  Same operation and arguments as
  * b200_sgemm plus the number of K slices (>= 2); the partial sums live in a fixed
- * B200_SGEMM_STATIC_SCRATCH_BYTES array inside the library, which every GPU that loads the library
- * holds until the process exits.  The call allocates nothing.  split_k * M * N * 4 bytes must fit the
- * array, else B200_SGEMM_SCRATCH_LIMIT is returned and nothing runs.  The first call on a device
- * resolves the array's device address; make that call before any stream capture on the device.  All
+ * B200_SGEMM_STATIC_SCRATCH_BYTES array inside the library's device image, which every GPU the entry point
+ * was called on holds until the process exits.  The call itself calls no allocation routine.  split_k * M * N * 4
+ * bytes must fit the array, else B200_SGEMM_SCRATCH_LIMIT is returned and nothing runs.  The first call on a
+ * device resolves the array's device address, and with CUDA's default lazy module loading that is also the
+ * moment the driver loads the module and reserves the array (free device memory drops by about the array's size
+ * during that one call; later calls leave it unchanged): make that first call in the host's initialisation phase,
+ * before any stream capture on the device, or run with CUDA_MODULE_LOADING=EAGER.  All
  * calls share the array (it keeps the previous call's contents; no part of it needs clearing because
  * every slice is fully written before it is read), so calls that can overlap on the GPU race: keep them
  * on one stream or order them with events.

@@ -6,7 +6,7 @@ generated kernel translation units in parallel, link
 
     rocm_sgemm_b200/libb200_sgemm.so          the C ABI of include/b200_sgemm.h
     rocm_sgemm_b200/libb200_cublas_wrapper.so the vendor-BLAS comparison column (links cuBLAS)
-    rocm_sgemm_b200/bin/gemm_test, gemm_bench the C++ harnesses (harness/)
+    rocm_sgemm_b200/bin/gemm_test, gemm_bench, cublas_test, cublas_bench   the C++ harnesses (harness/)
 
 Objects are cached under rocm_sgemm_b200/build/ keyed by a hash of the source, the headers it
 includes and the flags, so an unchanged kernel is not recompiled.
@@ -60,13 +60,14 @@ def _digest(paths, flags) -> str:
     return h.hexdigest()[:16]
 
 
-def _compile(src: Path, deps, flags, verbose=False, ptxas_log: Path | None = None) -> Path:
+def _compile(src: Path, deps, flags, verbose=False, ptxas_log: Path | None = None, stem: str | None = None) -> Path:
     BUILD.mkdir(exist_ok=True)
     tag = _digest([src] + list(deps), flags)
-    obj = BUILD / f"{src.stem}.{tag}.o"
+    stem = stem or src.stem
+    obj = BUILD / f"{stem}.{tag}.o"
     if obj.exists():
         return obj
-    for old in BUILD.glob(f"{src.stem}.*.o"):
+    for old in BUILD.glob(f"{stem}.*.o"):
         old.unlink()
     cmd = [nvcc()] + flags + ["-Xptxas", "-v", "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True, env=_env())
@@ -136,14 +137,19 @@ def build_harness(verbose=False):
     BIN.mkdir(exist_ok=True)
     outs = []
     hdir = PKG / "harness"
-    for name in ("gemm_test", "gemm_bench"):
-        src = hdir / f"{name}.cu"
+    # cublas_test / cublas_bench: the same sources restricted to the vendor column (the reference's
+    # test_rocblas / bench_rocblas targets, test/CMakeLists.txt:11, benchmark/CMakeLists.txt:11)
+    for name, srcname, defs in (("gemm_test", "gemm_test", []), ("gemm_bench", "gemm_bench", []),
+                                ("cublas_test", "gemm_test", ["-DHARNESS_VENDOR_ONLY"]),
+                                ("cublas_bench", "gemm_bench", ["-DHARNESS_VENDOR_ONLY"])):
+        src = hdir / f"{srcname}.cu"
         if not src.exists():
             continue
         deps = [p for p in hdir.glob("*.hpp")] + [REPO / "include" / "rocm_sgemm" / "gemm.hpp",
-                                                  REPO / "include" / "b200_sgemm.h"]
-        flags = NVCC_FLAGS + ["-I", str(REPO / "include"), "-I", str(hdir), "-Xcompiler", "-fopenmp"]
-        obj = _compile(src, deps, flags, verbose)
+                                                  REPO / "include" / "b200_sgemm.h",
+                                                  REPO / "include" / "b200_cublas_wrapper.h"]
+        flags = NVCC_FLAGS + defs + ["-I", str(REPO / "include"), "-I", str(hdir), "-Xcompiler", "-fopenmp"]
+        obj = _compile(src, deps, flags, verbose, stem=name)
         exe = BIN / name
         cmd = [nvcc()] + ARCH_FLAGS + ["-o", str(exe), str(obj), "-L", str(PKG), "-lb200_sgemm",
                                        "-lb200_cublas_wrapper", "-lcublas", "-Xlinker", "-rpath", "-Xlinker",
@@ -151,15 +157,6 @@ def build_harness(verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True, env=_env())
         if r.returncode != 0:
             raise RuntimeError(f"link failed for {name}:\n{r.stderr[-4000:]}")
-        outs.append(exe)
-    # stand-alone probe of the packed-FMA inner loop (no library needed)
-    psrc = hdir / "inner_loop_probe.cu"
-    if psrc.exists():
-        obj = _compile(psrc, [], NVCC_FLAGS, verbose)
-        exe = BIN / "inner_loop_probe"
-        r = subprocess.run([nvcc()] + ARCH_FLAGS + ["-o", str(exe), str(obj)], capture_output=True, text=True, env=_env())
-        if r.returncode != 0:
-            raise RuntimeError(f"link failed for inner_loop_probe:\n{r.stderr[-4000:]}")
         outs.append(exe)
     # the tuner's one-trial executable (loads a candidate build of the library with dlopen)
     tsrc = PKG / "config" / "tuner.cpp"

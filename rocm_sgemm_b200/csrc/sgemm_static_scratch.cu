@@ -7,23 +7,32 @@
 // somebody else's budget; a service thread with a latency bound that must not enter the driver's
 // allocator, which takes a device-wide lock and can synchronise the device; a plug-in whose host
 // forbids device allocation outside an init hook that the plug-in cannot extend.  For them the scratch
-// is a fixed array in device global memory that exists as soon as the library is loaded.
+// is a fixed array in device global memory that belongs to the library's own image.
 //
-// What it costs.  B200_SGEMM_STATIC_SCRATCH_BYTES (32 MiB) of device memory on every GPU whose context
-// loads this library, held until the process exits, whether or not the entry point is ever called.
+// What it costs, and when.  B200_SGEMM_STATIC_SCRATCH_BYTES (32 MiB) of device memory on every GPU on which the
+// entry point has been called, held until the process exits.  The memory is reserved when the CUDA runtime loads
+// this file's module on the device.  With CUDA 12's default (lazy module loading) that happens at the first use of
+// the module on that device, which is the first call of this entry point there: that one call makes the driver
+// reserve the 32 MiB (free device memory drops by that much, and the call can fail with an out-of-memory error
+// on a device that has none left), every later call finds the array in place and leaves free memory exactly as it
+// was.  A host that may not touch the allocator later must therefore make one call per device inside its
+// initialisation phase (any small problem will do), or start the process with CUDA_MODULE_LOADING=EAGER, which moves
+// the reservation to the creation of the device's context.  The cached device address does not survive
+// cudaDeviceReset().
 //
 // Rules for callers.
 //   * splits x M x N x 4 bytes must fit the array; otherwise the call is rejected with
 //     B200_SGEMM_SCRATCH_LIMIT and nothing is launched.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and
-//     caches it.  That lookup is a runtime call that initialises the module on the device; make the
-//     first call on a device before starting any stream capture on it.
+//     caches it.  That lookup is a runtime call that loads the module on the device (see above); make the
+//     first call on a device during initialisation and before starting any stream capture on it.
 //   * All calls on a device share the one array, and the array keeps whatever the previous call left in
 //     it.  Nothing has to start at zero: every K slice overwrites its whole M x N partial before the
 //     reduction reads it.  Two calls whose kernels can overlap on the GPU (different streams, no event
 //     between them) race on the array and corrupt each other's result; order them on one stream or with
 //     events.
-//   * No cudaMalloc, cudaFree, cudaMallocAsync or other allocating routine is reached from here.
+//   * No cudaMalloc, cudaFree, cudaMallocAsync or other allocating routine is reached from here; the only
+//     memory the driver ever sets aside on behalf of this entry point is the array itself, once per device.
 #include "../../include/b200_sgemm.h"
 
 #include <cuda_runtime.h>

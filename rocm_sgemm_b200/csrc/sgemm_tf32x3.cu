@@ -436,10 +436,12 @@ __global__ void __launch_bounds__(T_THREADS, 1)
 // A K-contiguous operand whose pitch is not a multiple of 16 bytes (K % 4 != 0) or whose base is misaligned is copied
 // into R rows of Kp floats (zero padded from K to Kp).  Operands that are not K-contiguous go through the library's
 // transposition (launch_transpose) instead.
+// One-dimensional grid (k-blocks fastest): neither extent is bound by the 65535 limit of gridDim.y.
 __global__ void __launch_bounds__(256) repack_kernel(float* __restrict__ dst, const float* __restrict__ src, int R, int K,
-                                                     int Kp)
+                                                     int Kp, unsigned k_blocks)
 {
-    const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+    const unsigned rb = blockIdx.x / k_blocks;
+    const int      r0 = (int)rb * 32, k0 = (int)(blockIdx.x - rb * k_blocks) * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
     for(int i = ty; i < 32; i += 8)
     {
@@ -482,30 +484,51 @@ bool encode_kmajor(CUtensorMap* map, const float* base, size_t rows, size_t K, s
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// per device: facts looked up once.  per (device, stream): the repack buffers, so that calls on different
+// streams never share one (a second call's repack would overwrite what the first call's kernel still reads).
 struct Scratch
+{
+    int* status = nullptr;
+    int  sms = 0;
+    bool attr_set[2] = {false, false};
+};
+struct Repack
 {
     float* a = nullptr;
     float* b = nullptr;
     size_t bytes_a = 0, bytes_b = 0;
-    int*   status = nullptr;
-    int    sms = 0;
-    bool   attr_set[2] = {false, false};
 };
-std::mutex             g_mutex;
-std::map<int, Scratch> g_scratch;
+std::mutex                                     g_mutex;
+std::map<int, Scratch>                         g_scratch;
+std::map<std::pair<int, cudaStream_t>, Repack> g_repack;
 
-cudaError_t grow(float** p, size_t* have, size_t need)
+cudaError_t grow(float** p, size_t* have, size_t need, cudaStream_t stream)
 {
     if(*have >= need)
         return cudaSuccess;
     if(*p)
+    {
+        // kernels queued on this stream may still read the old block
+        cudaError_t e = cudaStreamSynchronize(stream);
+        if(e != cudaSuccess)
+            return e;
         cudaFree(*p);
+    }
     *p    = nullptr;
     *have = 0;
     cudaError_t e = cudaMalloc(p, need);
     if(e == cudaSuccess)
         *have = need;
     return e;
+}
+
+cudaError_t launch_repack(float* dst, const float* src, size_t R, size_t K, size_t Kp, cudaStream_t stream)
+{
+    const unsigned long long kb = (Kp + 31) / 32, rb = (R + 31) / 32;
+    if(kb * rb > 0x7fffffffull)
+        return cudaErrorInvalidConfiguration;
+    repack_kernel<<<(unsigned)(kb * rb), 256, 0, stream>>>(dst, src, (int)R, (int)K, (int)Kp, (unsigned)kb);
+    return cudaPeekAtLastError();
 }
 
 template<int BN>
@@ -545,6 +568,7 @@ extern "C" int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float
         return (int)e;
     std::lock_guard<std::mutex> lock(g_mutex);
     Scratch&                    s = g_scratch[device];
+    Repack&                     r = g_repack[std::make_pair(device, stream)];
     if(!s.status)
     {
         if((e = cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return (int)e;
@@ -557,27 +581,29 @@ extern "C" int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float
     const float* b_src    = B;
     if(!a_direct)
     {
-        if((e = grow(&s.a, &s.bytes_a, M * Kp * sizeof(float))) != cudaSuccess) return (int)e;
+        if((e = grow(&r.a, &r.bytes_a, M * Kp * sizeof(float), stream)) != cudaSuccess) return (int)e;
         if(layout_a == B200_SGEMM_ROW_MAJOR) // K-contiguous already: copy with the padded pitch
         {
-            dim3 grid((unsigned)((Kp + 31) / 32), (unsigned)((M + 31) / 32));
-            repack_kernel<<<grid, 256, 0, stream>>>(s.a, A, (int)M, (int)K, (int)Kp);
+            if((e = launch_repack(r.a, A, M, K, Kp, stream)) != cudaSuccess) return (int)e;
         }
         else // col-major A = K rows of M contiguous floats -> M rows of K (the pad columns are never read)
-            launch_transpose(A, s.a, K, M, M, Kp, stream);
-        a_src = s.a;
+        {
+            if((e = launch_transpose(A, r.a, K, M, M, Kp, stream)) != cudaSuccess) return (int)e;
+        }
+        a_src = r.a;
     }
     if(!b_direct)
     {
-        if((e = grow(&s.b, &s.bytes_b, N * Kp * sizeof(float))) != cudaSuccess) return (int)e;
+        if((e = grow(&r.b, &r.bytes_b, N * Kp * sizeof(float), stream)) != cudaSuccess) return (int)e;
         if(layout_b == B200_SGEMM_COL_MAJOR)
         {
-            dim3 grid((unsigned)((Kp + 31) / 32), (unsigned)((N + 31) / 32));
-            repack_kernel<<<grid, 256, 0, stream>>>(s.b, B, (int)N, (int)K, (int)Kp);
+            if((e = launch_repack(r.b, B, N, K, Kp, stream)) != cudaSuccess) return (int)e;
         }
         else // row-major B = K rows of N contiguous floats -> N rows of K
-            launch_transpose(B, s.b, K, N, N, Kp, stream);
-        b_src = s.b;
+        {
+            if((e = launch_transpose(B, r.b, K, N, N, Kp, stream)) != cudaSuccess) return (int)e;
+        }
+        b_src = r.b;
     }
     if((e = cudaPeekAtLastError()) != cudaSuccess)
         return (int)e;
@@ -618,13 +644,13 @@ extern "C" int b200_sgemm_3xtf32_shutdown(void)
     std::lock_guard<std::mutex> lock(g_mutex);
     int                         saved = 0;
     cudaGetDevice(&saved);
-    for(auto& kv : g_scratch)
+    for(auto& kv : g_repack)
     {
-        cudaSetDevice(kv.first);
+        cudaSetDevice(kv.first.first);
         cudaFree(kv.second.a);
         cudaFree(kv.second.b);
     }
-    g_scratch.clear();
+    g_repack.clear();
     cudaSetDevice(saved);
     return B200_SGEMM_OK;
 }

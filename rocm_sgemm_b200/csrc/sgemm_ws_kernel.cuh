@@ -15,8 +15,17 @@
 //     blocks with 128-bit loads, transposed in registers and stored with an XOR swizzle that keeps both
 //     those stores and the consumers' 128-bit reads free of bank conflicts.  Operands that do not meet
 //     TMA's alignment rules fall back to guarded cp.async in the same warps.
-//   * the CTA is persistent: it walks work units (tile, K-slice) blockIdx.x, +gridDim.x, ... and the
-//     producers run ahead into the next unit while the consumers store C.
+//   * the CTA is persistent and the producers run ahead into the next piece of work while the consumers store C.
+//     Two schedules (WsArgs::sched):
+//       0  work units (tile, K slice) dealt round-robin: blockIdx.x, +gridDim.x, ...
+//       1  the tiles' K tiles, laid end to end in tile order, are cut into gridDim.x equal contiguous ranges, one
+//          per CTA, so every CTA does the same amount of work whatever the tile count (no partly filled last wave).
+//          A range starts inside one tile and ends inside another.  The CTA computes the HEAD of its last tile first
+//          (k from 0) and parks the accumulators in global memory; it finishes with the TAIL of its first tile, whose
+//          accumulators it takes over from the neighbour that computed that tile's head at the very start of the
+//          kernel.  Every C element is therefore still ONE k-ascending FMA chain (bit-identical to schedule 0
+//          without split-K); the chain merely changes hands once.  Needs ranges of at least one whole tile
+//          (tiles >= CTAs), so that no tile is shared by more than two CTAs.
 //
 // Packed FMA: the B fragment supplies natural pairs of neighbouring columns (64-bit halves of the
 // 128-bit shared-memory read), the A value is duplicated into both halves.  The FMA order keeps the pair
@@ -44,6 +53,7 @@ constexpr uint64_t WS_WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull; // one second
 // status word values written by the kernel (0 = ok)
 constexpr int WS_ERR_FULL_TIMEOUT  = 1; // a consumer gave up waiting for a stage to fill
 constexpr int WS_ERR_EMPTY_TIMEOUT = 2; // a producer gave up waiting for a stage to drain
+constexpr int WS_ERR_PEER_TIMEOUT  = 3; // a consumer gave up waiting for the neighbour CTA's parked accumulators
 
 struct WsArgs
 {
@@ -56,6 +66,96 @@ struct WsArgs
     // folds the all-gather that follows a column-sharded product into the epilogue.  Only without split-K.
     int      n_extra;
     float*   extra_c[WS_MAX_EXTRA];
+    // schedule 1 (see the head of this file)
+    int       sched;
+    int       k_tiles;  // K tiles per tile: ceil(K / block_k)
+    float*    handover; // gridDim.x slots of block_m x block_n floats: slot c holds what CTA c parked
+    unsigned* flags;    // one word per (CTA, consumer warp): == epoch once that warp's part of slot c is complete
+    unsigned  epoch;    // differs from launch to launch, so the words never need clearing
+};
+
+// One contiguous piece of work of a CTA: K range [k_begin, k_end) of one tile.
+struct WsPiece
+{
+    int tile_id;
+    int k_begin, k_end;
+    int split; // schedule 0: index of the K slice (selects the partial-sum matrix)
+    int recv;  // >= 0: start from the accumulators parked in this slot instead of zero
+    int send;  // >= 0: park the accumulators in this slot instead of storing C
+};
+
+// The list of pieces of this CTA, identical for its producer and consumer threads.
+struct WsSchedule
+{
+    int n;
+    int sched, tiles, stride, first;              // schedule 0
+    int head_tile, head_kt, whole0, tail_kt, kts; // schedule 1
+    int bk, K, k_per_split;
+
+    __device__ __forceinline__ void init(const WsArgs& w, int tiles_, int BK)
+    {
+        sched = w.sched;
+        tiles = tiles_;
+        bk    = BK;
+        K     = w.g.K;
+        k_per_split = w.g.k_per_split;
+        if(sched == 0)
+        {
+            first  = blockIdx.x;
+            stride = gridDim.x;
+            n      = first < w.total_units ? (w.total_units - first + stride - 1) / stride : 0;
+        }
+        else
+        {
+            kts = w.k_tiles;
+            const long long units = (long long)tiles * kts;
+            const long long u0    = units * blockIdx.x / gridDim.x;
+            const long long u1    = units * (blockIdx.x + 1) / gridDim.x;
+            const int       x     = (int)(u0 / kts);
+            tail_kt               = (int)(u0 - (long long)x * kts); // > 0: the range starts inside tile x
+            head_tile             = (int)(u1 / kts);
+            head_kt               = (int)(u1 - (long long)head_tile * kts); // > 0: the range ends inside head_tile
+            whole0                = tail_kt > 0 ? x + 1 : x;
+            n                     = (head_kt > 0 ? 1 : 0) + (head_tile - whole0) + (tail_kt > 0 ? 1 : 0);
+        }
+    }
+    __device__ __forceinline__ WsPiece piece(int i) const
+    {
+        WsPiece p;
+        p.recv = p.send = -1;
+        p.split = 0;
+        if(sched == 0)
+        {
+            const int unit = first + i * stride;
+            p.split        = unit / tiles;
+            p.tile_id      = unit - p.split * tiles;
+            p.k_begin      = p.split * k_per_split;
+            p.k_end        = min(K, p.k_begin + k_per_split);
+            return p;
+        }
+        const int h = head_kt > 0 ? 1 : 0;
+        if(h && i == 0)
+        {
+            p.tile_id = head_tile; // first of all: the head of the last tile, parked for the next CTA
+            p.k_begin = 0;
+            p.k_end   = head_kt * bk; // < K: a head never reaches the last K tile
+            p.send    = blockIdx.x;
+        }
+        else if(i - h < head_tile - whole0)
+        {
+            p.tile_id = whole0 + (i - h);
+            p.k_begin = 0;
+            p.k_end   = K;
+        }
+        else
+        {
+            p.tile_id = whole0 - 1; // last of all: the tail of the first tile, continued from the previous CTA
+            p.k_begin = tail_kt * bk;
+            p.k_end   = K;
+            p.recv    = blockIdx.x - 1;
+        }
+        return p;
+    }
 };
 
 // ---- mbarrier / TMA helpers ------------------------------------------------------------------------
@@ -88,6 +188,19 @@ __device__ __forceinline__ uint64_t global_timer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Same poll, but the hardware may park the thread for up to `hint_ns` nanoseconds while the phase is incomplete
+// (instead of returning at once), so that a thread that waits long executes few instructions.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity), "r"(hint_ns)
+                 : "memory");
+    return ok != 0;
+}
 // Bounded wait.  The common case (the phase already completed) is one poll; otherwise poll for at most
 // WS_WAIT_LIMIT_NS of wall-clock time and at most WS_SPIN_LIMIT polls, looking at the CTA's abort flag
 // now and then.  false = gave up.
@@ -104,6 +217,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             return false;
     }
     return false;
+}
+// The producers' form of the bounded wait: they run stages ahead of the consumers, so they can afford to be
+// parked by the hardware between polls.  Every instruction a waiting warp executes is an issue slot taken from the
+// FMA stream of the consumer warps on the same scheduler; a parked poll executes a handful per microsecond.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    if(mbar_try_wait(bar, parity))
+        return true;
+    const uint64_t t0 = global_timer_ns();
+    for(uint32_t i = 0; i < WS_SPIN_LIMIT; ++i)
+    {
+        if(mbar_try_wait_parked(bar, parity, 1000u))
+            return true;
+        if((i & 7u) == 7u && (*abort_flag || global_timer_ns() - t0 > WS_WAIT_LIMIT_NS))
+            return false;
+    }
+    return false;
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v)
+{
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // tile copy global -> shared; (c0, c1) are element coordinates, c0 along the contiguous dimension
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
@@ -176,7 +316,9 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     {
         for(int s = 0; s < STAGES; ++s)
         {
-            mbar_init(full_bar(s), L::PRODUCERS + 1);
+            // arrivals per fill: the thread that arms the byte count (and issues the TMA copies), plus one per
+            // producer warp when an operand is staged by hand
+            mbar_init(full_bar(s), (w.tma_a && w.tma_b) ? 1 : L::PRODUCERS / 32 + 1);
             mbar_init(empty_bar(s), CONSUMER_WARPS);
         }
         *abort_flag = 0;
@@ -197,23 +339,27 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
         OperandStager<L::PRODUCERS, BM, BK, A_KMAJOR, ALIGNED> stage_a;
         OperandStager<L::PRODUCERS, BN, BK, B_KMAJOR, ALIGNED> stage_b;
         const bool manual_a = !w.tma_a, manual_b = !w.tma_b;
-        // TMA-only launches leave nothing to do for the other producer threads: they arrive once per stage
+        // Both operands by TMA: one thread does everything, the other producer threads leave at once.  (A warp
+        // that merely polled a barrier would still take issue slots from the consumers on its scheduler.)
+        if(!manual_a && !manual_b && ptid != 0)
+            return;
         int      s     = 0; // ring position
         uint32_t phase = 0; // parity of the current lap
-        for(int unit = blockIdx.x; unit < w.total_units; unit += gridDim.x)
+        WsSchedule sch;
+        sch.init(w, tiles, BK);
+        for(int pi = 0; pi < sch.n; ++pi)
         {
-            const int split   = unit / tiles;
-            const int tile_id = unit - split * tiles;
-            int       tile_m, tile_n;
-            map_tile<Cfg::RASTER>(tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
+            const WsPiece pc = sch.piece(pi);
+            int           tile_m, tile_n;
+            map_tile<Cfg::RASTER>(pc.tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
             const int m0 = tile_m * BM, n0 = tile_n * BN;
-            const int k_begin = split * p.k_per_split;
-            const int k_end   = min(p.K, k_begin + p.k_per_split);
+            const int k_begin = pc.k_begin;
+            const int k_end   = pc.k_end;
             const int ntiles  = (k_end - k_begin + BK - 1) / BK;
             for(int t = 0; t < ntiles; ++t)
             {
                 // the stage was released `phase` laps ago; the very first lap passes immediately
-                if(!mbar_wait(empty_bar(s), phase ^ 1u, abort_flag))
+                if(!mbar_wait_parked(empty_bar(s), phase ^ 1u, abort_flag))
                 {
                     if(!*abort_flag)
                     {
@@ -253,7 +399,12 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     cp_async_commit();
                     cp_async_wait<0>(); // guarded-copy fallback of an operand TMA could not take
                 }
-                mbar_arrive(full_bar(s)); // release: this thread's stores to the stage are done
+                if(manual_a || manual_b)
+                {
+                    __syncwarp(); // the warp's stores to the stage are done; one lane publishes them
+                    if((ptid & 31) == 0)
+                        mbar_arrive(full_bar(s));
+                }
                 if(++s == STAGES)
                 {
                     s = 0;
@@ -310,20 +461,75 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
 
     int      s     = 0;
     uint32_t phase = 0;
-    for(int unit = blockIdx.x; unit < w.total_units; unit += gridDim.x)
+    WsSchedule sch;
+    sch.init(w, tiles, BK);
+    // parked accumulators: slot c is block_m x block_n floats, thread-major in 16-byte units so that the accesses of
+    // a warp are contiguous; the reader is the thread with the same index in the next CTA
+    constexpr int ACC_VEC = TMT * TNT / 4;
+    for(int pi = 0; pi < sch.n; ++pi)
     {
-        const int split   = unit / tiles;
-        const int tile_id = unit - split * tiles;
-        int       tile_m, tile_n;
-        map_tile<Cfg::RASTER>(tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
+        const WsPiece pc = sch.piece(pi);
+        int           tile_m, tile_n;
+        map_tile<Cfg::RASTER>(pc.tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
         const int m0 = tile_m * BM, n0 = tile_n * BN;
-        const int k_begin = split * p.k_per_split;
-        const int k_end   = min(p.K, k_begin + p.k_per_split);
+        const int k_begin = pc.k_begin;
+        const int k_end   = pc.k_end;
         const int ntiles  = (k_end - k_begin + BK - 1) / BK;
 
         float    acc[MODE == FMA_SCALAR ? TMT : 1][MODE == FMA_SCALAR ? TNT : 1];
         uint64_t acc2[MODE == FMA_SCALAR ? 1 : TMT][MODE == FMA_SCALAR ? 1 : TNT / 2];
-        if constexpr(MODE == FMA_SCALAR)
+        if(pc.recv >= 0)
+        {
+            // the chain of this tile was started by the previous CTA (first thing it did): take its accumulators over
+            const unsigned* flag = w.flags + pc.recv * CONSUMER_WARPS + warp_id;
+            bool            got  = ld_acquire_u32(flag) == w.epoch;
+            if(!got)
+            {
+                const uint64_t t0 = global_timer_ns();
+                for(uint32_t it = 0; it < WS_SPIN_LIMIT && !got; ++it)
+                {
+                    __nanosleep(100);
+                    got = ld_acquire_u32(flag) == w.epoch;
+                    if(!got && (it & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > WS_WAIT_LIMIT_NS))
+                        break;
+                }
+            }
+            if(!got)
+            {
+                if(!*abort_flag)
+                {
+                    *abort_flag = 1;
+                    atomicCAS(w.status, 0, WS_ERR_PEER_TIMEOUT);
+                }
+                return;
+            }
+            const float4* src = reinterpret_cast<const float4*>(w.handover + (size_t)pc.recv * (BM * BN)) + tid;
+            float         c0[TMT][TNT];
+#pragma unroll
+            for(int v = 0; v < ACC_VEC; ++v)
+            {
+                const float4 q = __ldcg(src + v * Cfg::BLOCK_SIZE);
+                float*       d = &c0[0][0] + 4 * v;
+                d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
+            }
+            if constexpr(MODE == FMA_SCALAR)
+            {
+#pragma unroll
+                for(int i = 0; i < TMT; ++i)
+#pragma unroll
+                    for(int j = 0; j < TNT; ++j)
+                        acc[i][j] = c0[i][j];
+            }
+            else
+            {
+#pragma unroll
+                for(int i = 0; i < TMT; ++i)
+#pragma unroll
+                    for(int j = 0; j < TNT / 2; ++j)
+                        acc2[i][j] = pack2(c0[i][2 * j], c0[i][2 * j + 1]);
+            }
+        }
+        else if constexpr(MODE == FMA_SCALAR)
         {
 #pragma unroll
             for(int i = 0; i < TMT; ++i)
@@ -459,7 +665,27 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                 for(int j = 0; j < TNT / 2; ++j)
                     unpack2(acc2[i][j], c[i][2 * j], c[i][2 * j + 1]);
         }
-        store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)split * p.split_stride, m0 + tm0, n0 + tn0);
+        if(pc.send >= 0)
+        {
+            // park the accumulators for the CTA that continues this tile, then publish them warp by warp (the reader
+            // of a thread's values is the thread with the same index, so a warp only ever waits for its namesake and
+            // no block-wide barrier is needed): the warp's stores -> __syncwarp -> one lane's gpu-scope release
+            float4* dst = reinterpret_cast<float4*>(w.handover + (size_t)pc.send * (BM * BN)) + tid;
+#pragma unroll
+            for(int v = 0; v < ACC_VEC; ++v)
+            {
+                const float* q = &c[0][0] + 4 * v;
+                __stcg(dst + v * Cfg::BLOCK_SIZE, make_float4(q[0], q[1], q[2], q[3]));
+            }
+            __syncwarp();
+            if(lane == 0)
+            {
+                __threadfence();
+                st_release_u32(w.flags + pc.send * CONSUMER_WARPS + warp_id, w.epoch);
+            }
+            continue;
+        }
+        store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)pc.split * p.split_stride, m0 + tm0, n0 + tn0);
         for(int d = 0; d < w.n_extra; ++d) // plain stores; to a peer GPU's memory when the pointer is a peer mapping
             store_tile<Cfg, LC, ALIGNED>(c, p, w.extra_c[d], m0 + tm0, n0 + tn0);
     }

@@ -8,7 +8,8 @@
 // --iters / --warmup (fixed launch counts instead of Google Benchmark's adaptive count), --identity (B =
 // identity and a bit-exact check of C == A: the identity-multiply methodology), --cpu ROWS (time the
 // host verification GEMM on ROWS rows and print its GFLOP/s and thread count), --json (one JSON object
-// per row on stdout).
+// per row on stdout), --vendor-only (time cublasSgemm alone: the rows of the reference's
+// benchmark/rocblas/bench.cpp:43-123; the default of the `cublas_bench` build, -DHARNESS_VENDOR_ONLY).
 #include "harness.hpp"
 
 #include <b200_cublas_wrapper.h>
@@ -56,6 +57,11 @@ struct options
     int    batch_count = 1;
     int    iters = 100, warmup = 10;
     bool   identity = false, json = false, vendor = true, tf32x3 = false;
+#ifdef HARNESS_VENDOR_ONLY
+    bool   vendor_only = true;
+#else
+    bool   vendor_only = false;
+#endif
     size_t cpu_rows = 0;
 };
 
@@ -110,6 +116,7 @@ void usage(const char* prog)
                 "  --identity          B = identity, verify C == A bit for bit\n"
                 "  --cpu <rows>        also time the host GEMM on <rows> rows of C\n"
                 "  --no-vendor         skip the cuBLAS column      --json   machine-readable rows\n"
+                "  --vendor-only       time cublasSgemm alone (what cublas_bench does by default)\n"
                 "  --tf32x3            also time the optional 3xTF32 tensor-core entry (its own column)\n",
                 prog);
 }
@@ -162,6 +169,7 @@ int main(int argc, char** argv)
         else if(a == "--cpu") opt.cpu_rows = std::stoul(next());
         else if(a == "--json") opt.json = true;
         else if(a == "--no-vendor") opt.vendor = false;
+        else if(a == "--vendor-only") opt.vendor_only = true;
         else if(a == "--tf32x3") opt.tf32x3 = true;
         else if(a == "--help") { usage(argv[0]); return 0; }
         else std::fprintf(stderr, "ignoring unknown argument %s\n", a.c_str());
@@ -175,9 +183,13 @@ int main(int argc, char** argv)
     CUDA_CHECK(cudaDeviceGetAttribute(&clock_khz, cudaDevAttrClockRate, device));
     // FP32 non-tensor peak: SMs x 128 lanes x 2 flops x clock
     const double peak_tflops = prop.multiProcessorCount * 128.0 * 2.0 * clock_khz * 1e3 * 1e-12;
+    if(opt.vendor_only)
+        opt.vendor = true;
     if(opt.vendor && !b200_cublas_init())
     {
         std::fprintf(stderr, "cuBLAS initialisation failed; vendor column disabled\n");
+        if(opt.vendor_only)
+            return 1;
         opt.vendor = false;
     }
     if(!opt.json)
@@ -222,7 +234,12 @@ int main(int argc, char** argv)
             const double flops = 2.0 * M * N * K * bc;
             const stats  ours  = time_launches(
                 [&] {
-                    if(bc == 1)
+                    if(opt.vendor_only)
+                    {
+                        for(size_t b = 0; b < bc; ++b)
+                            b200_cublas_gemm_layout(lc, la, lb, dC + b * M * N, dA + b * M * K, dB + b * K * N, M, N, K, stream);
+                    }
+                    else if(bc == 1)
                         table[idx](dC, dA, dB, M, N, K, stream);
                     else if(b200_sgemm_strided_batched(lc, la, lb, dC, dA, dB, M, N, K, M * N, M * K, K * N, bc, stream)
                             != B200_SGEMM_OK)
@@ -246,7 +263,9 @@ int main(int argc, char** argv)
                 failures += !exact;
             }
             stats vendor;
-            if(opt.vendor)
+            if(opt.vendor_only)
+                vendor = ours;
+            else if(opt.vendor)
                 vendor = time_launches(
                     [&] {
                         for(size_t b = 0; b < bc; ++b)
@@ -254,7 +273,7 @@ int main(int argc, char** argv)
                     },
                     stream, flops, opt.warmup, opt.iters);
             stats tensor; // the optional 3xTF32 tensor-core entry: its own column, not the graded arithmetic
-            if(opt.tf32x3)
+            if(opt.tf32x3 && !opt.vendor_only)
                 tensor = time_launches(
                     [&] {
                         for(size_t b = 0; b < bc; ++b)

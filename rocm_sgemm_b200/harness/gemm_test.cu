@@ -4,9 +4,14 @@
 // and each of its 13 shapes, inputs from mt19937(1) re-seeded per matrix, one rocm_sgemm::gemm call,
 // comparison of every element against the host GEMM with absolute tolerance 1e-4.  Added on top: the
 // identity-multiply check (C must equal A bit for bit) and two ragged shapes, which the reference's
-// unguarded loads could not pass.  Exit code 0 only if everything passed.
+// unguarded loads could not pass.  A third group, CublasTest, holds the vendor wrapper to the same bar, as the
+// reference's test/rocblas/test.cpp:31-186 does for its rocBLAS wrapper (13 shapes, 1e-4 against the host GEMM;
+// here for all eight layouts, the reference covers the four with a column-major C).  Built a second time with
+// -DHARNESS_VENDOR_ONLY as `cublas_test`, which runs that group alone (the reference's test_rocblas target,
+// test/CMakeLists.txt:11).  Exit code 0 only if everything passed.
 #include "harness.hpp"
 
+#include <b200_cublas_wrapper.h>
 #include <rocm_sgemm/gemm.hpp>
 
 #include <cmath>
@@ -123,6 +128,34 @@ bool verify_blas(size_t M, size_t N, size_t K, cudaStream_t stream)
             }
     return true;
 }
+
+// The vendor wrapper behind the comparison column: cublasSgemm in strict FP32 for layout (la, lb, lc).
+bool verify_cublas(int la, int lb, int lc, size_t M, size_t N, size_t K, cudaStream_t stream)
+{
+    host_matrix hA(M, K, (layout)la), hB(K, N, (layout)lb), hC(M, N, (layout)lc), hRef(M, N, (layout)lc);
+    fill_like_reference_test(hA);
+    fill_like_reference_test(hB);
+    device_buffers d(hA.bytes(), hB.bytes(), hC.bytes());
+    CUDA_CHECK(cudaMemcpy(d.A, hA.data(), hA.bytes(), cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemcpy(d.B, hB.data(), hB.bytes(), cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemset(d.C, 0xff, hC.bytes()));
+    if(b200_cublas_gemm_layout(lc, la, lb, d.C, d.A, d.B, M, N, K, stream) != 0)
+    {
+        std::printf("    cublasSgemm returned an error\n");
+        return false;
+    }
+    CUDA_CHECK(cudaDeviceSynchronize());
+    CUDA_CHECK(cudaMemcpy(hC.data(), d.C, hC.bytes(), cudaMemcpyDeviceToHost));
+    host_sgemm(hRef, hA, hB, 0, M);
+    for(size_t i = 0; i < M; ++i)
+        for(size_t j = 0; j < N; ++j)
+            if(!(std::fabs(hC(i, j) - hRef(i, j)) <= 1e-4f))
+            {
+                std::printf("    mismatch at (%zu,%zu): %.9g vs %.9g\n", i, j, hC(i, j), hRef(i, j));
+                return false;
+            }
+    return true;
+}
 } // namespace
 
 int main()
@@ -133,6 +166,7 @@ int main()
     cudaStream_t stream;
     CUDA_CHECK(cudaStreamCreate(&stream));
     int run = 0, failed = 0;
+#ifndef HARNESS_VENDOR_ONLY
     for(int la = 0; la < 2; ++la)
         for(int lb = 0; lb < 2; ++lb)
             for(int lc = 0; lc < 2; ++lc)
@@ -163,6 +197,30 @@ int main()
             failed += !ok[i];
             std::printf("[%s] BlasWrapperTest/%s.Size%zux%zux%zu\n", ok[i] ? "  OK  " : "FAILED", names[i], s[0], s[1], s[2]);
         }
+    }
+#endif
+    if(!b200_cublas_init())
+    {
+        std::printf("[FAILED] CublasTest: cuBLAS initialisation failed\n");
+        ++run;
+        ++failed;
+    }
+    else
+    {
+        for(int la = 0; la < 2; ++la)
+            for(int lb = 0; lb < 2; ++lb)
+                for(int lc = 0; lc < 2; ++lc)
+                    for(int i = 0; i < 13; ++i) // the reference suite's 13 shapes
+                    {
+                        const auto& s  = shapes[i];
+                        const bool  ok = verify_cublas(la, lb, lc, s[0], s[1], s[2], stream);
+                        ++run;
+                        failed += !ok;
+                        std::printf("[%s] CublasTest/%s%s%s.Size%zux%zux%zu\n", ok ? "  OK  " : "FAILED",
+                                    layout_letter((layout)la), layout_letter((layout)lb), layout_letter((layout)lc), s[0],
+                                    s[1], s[2]);
+                    }
+        b200_cublas_cleanup();
     }
     CUDA_CHECK(cudaStreamDestroy(stream));
     std::printf("%d tests, %d failed\n", run, failed);

@@ -27,6 +27,7 @@ def test_gemm_test_suite():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-1000:]
     assert tail.endswith(" 0 failed") and "FAILED" not in r.stdout
     assert "BlasWrapperTest/TT" in r.stdout and "IdentityBitExact512" in r.stdout
+    assert r.stdout.count("] CublasTest/") == 104  # the vendor column: 13 shapes x 8 layouts
 
 
 def test_gemm_bench_rows():
