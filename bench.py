@@ -11,6 +11,9 @@ One "step" is one GEMM through the library's C ABI.  Workloads (all FP32, synthe
                           K x N/G slice of B); no data-path collective.  An NCCL all-gather of C is timed
                           separately and reported as `allgather_ms`, outside `value`.
   c3:<abc>, c4:<MxNxK>    one layout of the 4096^3 all-layout configuration / one sweep shape.
+At 1 GPU the line also carries `all_layouts` (the eight layout permutations at 4096^3, TFLOP/s and % of the FP32
+peak each); at N > 1 rank 0 also times the unsharded workload on its own GPU (`single_gpu_same_workload_tflops`,
+`speedup_vs_single_gpu`).
 
 Prints ONE JSON line (rank 0).  `value` is whole-job TFLOPS with operands resident in HBM; `e2e` is the
 same metric through the same C ABI call with pinned HOST buffers, the host<->device copies inside the
@@ -199,7 +202,9 @@ def reference_arm(args, w):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 2.0 * M * N * K / (value * 1e12) * 1e3,
             "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": {"workload": w["name"], "desc": w["desc"]},
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["name"], "desc": w["desc"], "M": M, "N": N, "K": K,
+                       "layout_abc": "".join("rc"[x] for x in (w["la"], w["lb"], w["lc"]))},
             "cpu_baseline": info,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -248,10 +253,26 @@ def ours(args, w):
         hA, hBfull = host_inputs(w)
         dA = torch.from_numpy(hA).to(dev)
         dBfull = torch.from_numpy(hBfull).to(dev)
+    single_gpu = None
     if G > 1:
         from rocm_sgemm_b200 import sharded
+        if rank == 0:
+            # the same workload unsharded on one GPU, so that the N-GPU speed-up is formed on ONE workload in one run
+            dCfull = torch.empty(M * N, dtype=torch.float32, device=dev)
+            for _ in range(2):
+                sg.gemm(lc, la, lb, dCfull, dA, dBfull, M, N, K)
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(3):
+                sg.gemm(lc, la, lb, dCfull, dA, dBfull, M, N, K)
+            s1.record()
+            s1.synchronize()
+            single_gpu = {"ms_per_step": s0.elapsed_time(s1) / 3}
+            single_gpu["tflops"] = 2.0 * M * N * K / (single_gpu["ms_per_step"] * 1e-3) / 1e12
+            del dCfull
         dB = sharded.local_b_slice(dBfull, lb, K, N, G, rank)  # packed K x Nl slice of this rank
         del dBfull
+        torch.cuda.empty_cache()
     else:
         dB = dBfull
     dC = torch.empty(M * Nl, dtype=torch.float32, device=dev)
@@ -259,6 +280,7 @@ def ours(args, w):
     params, variant = sg.select_config(M, Nl, K, lc, la, lb)
     # GEMM kernel + split-K reduction + one transposition kernel per pre-transposed operand
     launches_per_step = 1 + (1 if params.split_k > 1 else 0) + bin(params.pretranspose).count("1")
+    launches_total = 0
 
     def step():
         sg.gemm(lc, la, lb, dC, dA, dB, M, Nl, K, stream=stream)
@@ -378,33 +400,7 @@ def ours(args, w):
     pcie_h2d_gbs = copy_gbs(dA, hA_t)
     pcie_d2h_gbs = copy_gbs(hC_t, dC)
 
-    def e2e_step():
-        # one blocking call of the C ABI with HOST buffers: upload, GEMM and download overlapped inside the library
-        sg.gemm_host(lc, la, lb, hC_t, hA_t, hB_t, M, Nl, K)
-
     submit_cpu_ms = []  # host time spent inside submit (it includes waiting for the slot of the job two steps back)
-
-    def e2e_stream(steps):
-        # the same call split into submit / wait, two jobs in flight: step i+1 is submitted before the result of
-        # step i is awaited, so its uploads overlap the compute-bound tail and the downloads of step i.  Every
-        # step uploads its A and B from pinned host memory and downloads its C (alternating host buffers).
-        pending = []
-        for i in range(steps):
-            t0 = time.perf_counter()
-            pending.append(sg.gemm_host_submit(lc, la, lb, hC_t if i % 2 == 0 else hC2_t, hA_t, hB_t, M, Nl, K))
-            submit_cpu_ms.append((time.perf_counter() - t0) * 1e3)
-            if len(pending) > 1:
-                sg.gemm_host_wait(pending.pop(0))
-        for t in pending:
-            sg.gemm_host_wait(t)
-
-    for _ in range(2):
-        e2e_step()
-    e2e_stream(2)
-    if w["init"] == "identity" and G == 1:
-        if not (torch.equal(hC_t.view(torch.int32), hA_t.view(torch.int32))
-                and torch.equal(hC2_t.view(torch.int32), hA_t.view(torch.int32))):
-            raise SystemExit("host-buffer entry: identity-multiply result differs from A")
 
     def timed(fn, steps):
         barrier()
@@ -418,16 +414,64 @@ def ours(args, w):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item() / steps
 
-    blocking_ms = timed(lambda n: [e2e_step() for _ in range(n)], max(3, e2e_steps // 2))
-    e2e_ms = timed(e2e_stream, e2e_steps)
+    if G == 1:
+        def e2e_step():
+            # one blocking call of the C ABI with HOST buffers: upload, GEMM and download overlapped inside the library
+            sg.gemm_host(lc, la, lb, hC_t, hA_t, hB_t, M, Nl, K)
+
+        def e2e_stream(steps):
+            # the same call split into submit / wait, two jobs in flight: step i+1 is submitted before the result of
+            # step i is awaited, so its uploads overlap the compute-bound tail and the downloads of step i.  Every
+            # step uploads its A and B from pinned host memory and downloads its C (alternating host buffers).
+            pending = []
+            for i in range(steps):
+                t0 = time.perf_counter()
+                pending.append(sg.gemm_host_submit(lc, la, lb, hC_t if i % 2 == 0 else hC2_t, hA_t, hB_t, M, Nl, K))
+                submit_cpu_ms.append((time.perf_counter() - t0) * 1e3)
+                if len(pending) > 1:
+                    sg.gemm_host_wait(pending.pop(0))
+            for t in pending:
+                sg.gemm_host_wait(t)
+
+        for _ in range(2):
+            e2e_step()
+        e2e_stream(2)
+        if w["init"] == "identity":
+            if not (torch.equal(hC_t.view(torch.int32), hA_t.view(torch.int32))
+                    and torch.equal(hC2_t.view(torch.int32), hA_t.view(torch.int32))):
+                raise SystemExit("host-buffer entry: identity-multiply result differs from A")
+        blocking_ms = timed(lambda n: [e2e_step() for _ in range(n)], max(3, e2e_steps // 2))
+        e2e_ms = timed(e2e_stream, e2e_steps)
+        h2d, d2h = (hA_t.numel() + hB_t.numel()) * 4, hC_t.numel() * 4
+        mode = "b200_sgemm_host_submit / _wait, two steps in flight (every step uploads A, B and downloads C)"
+        extra = {"blocking_call_ms": blocking_ms, "blocking_call_tflops": flops_total / (blocking_ms * 1e-3) / 1e12,
+                 "submit_cpu_ms_median": statistics.median(submit_cpu_ms[-e2e_steps:])}
+    else:
+        # column-sharded job from host memory: each rank uploads 1/G of the replicated A and its own B slice, the
+        # ranks all-gather A over NVLink, multiply, and download their C block; two steps in flight
+        pipe = sharded.ShardedHostGemm(sg, lc, la, lb, M, N, K, G, rank)
+
+        def e2e_stream(steps):
+            for i in range(steps):
+                pipe.submit(hC_t if i % 2 == 0 else hC2_t, hA_t, hB_t)
+            pipe.wait_all()
+
+        e2e_stream(2)
+        # the pipeline's result must be the device-resident result bit for bit
+        if not (torch.equal(hC_t.to(dev).view(torch.int32), dC.view(torch.int32))
+                and torch.equal(hC2_t.to(dev).view(torch.int32), dC.view(torch.int32))):
+            raise SystemExit("sharded host pipeline: result differs from the device-resident product")
+        e2e_ms = timed(e2e_stream, e2e_steps)
+        h2d, d2h = pipe.h2d_bytes * G, pipe.d2h_bytes * G
+        mode = ("sharded.ShardedHostGemm: per rank upload of 1/G of A and of its B slice, NCCL all-gather of A over "
+                "NVLink, b200_sgemm, download of the C block; two steps in flight")
+        extra = {"allgather_of_a_bytes_per_rank": (G - 1) * pipe.a_len * 4}
+        del pipe
     e2e = {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-           "steps": e2e_steps, "h2d_bytes_per_step": (hA_t.numel() + hB_t.numel()) * 4 * G,
-           "d2h_bytes_per_step": hC_t.numel() * 4 * G,
-           "mode": "b200_sgemm_host_submit / _wait, two steps in flight (every step uploads A, B and downloads C)",
-           "blocking_call_ms": blocking_ms, "blocking_call_tflops": flops_total / (blocking_ms * 1e-3) / 1e12,
-           "submit_cpu_ms_median": statistics.median(submit_cpu_ms[-e2e_steps:]),
+           "steps": e2e_steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "mode": mode,
            "pcie_h2d_gbs": pcie_h2d_gbs, "pcie_d2h_gbs": pcie_d2h_gbs,
-           "upload_bound_ms": (hA_t.numel() + hB_t.numel()) * 4 / (pcie_h2d_gbs * 1e9) * 1e3}
+           "upload_bound_ms": h2d / G / (pcie_h2d_gbs * 1e9) * 1e3}
+    e2e.update(extra)
 
     if rank != 0:
         if world > 1:
@@ -446,9 +490,8 @@ def ours(args, w):
                                "(clocks.max.sm); MEASURED_PEAKS.json has no FP32 non-tensor entry",
                 "peak_measured_fma_probe": probe, "frac_of_measured_probe": achieved / probe,
                 "achieved_at_min_time": flops_rank / (min_ms * 1e-3) / 1e12,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one sgemm_ws_kernel launch from the ncu capture
-                # summarised in profiles/sgemm_ws_kernel_4096cube_rrr.md (only this workload was captured)
-                "traffic": 390.9e6 if w["name"] == "c2" else None, "traffic_unit": "bytes per launch",
+                # DRAM traffic is a profiler counter: this run does not measure it
+                "traffic": None, "traffic_unit": "bytes per launch",
                 "algorithmic_flops_per_launch": flops_rank,
                 "algorithmic_bytes_per_launch": 4.0 * (M * K + K * Nl + M * Nl),
                 "achieved_hbm_gbs": 4.0 * (M * K + K * Nl + M * Nl) / (avg_ms * 1e-3) / 1e9}
@@ -479,6 +522,45 @@ def ours(args, w):
                   "note": "b200_sgemm_3xtf32: tcgen05 tensor-core path, FP32 split into two TF32 halves; "
                           "informational, not part of value/e2e"}
 
+    # ---- every layout permutation of the 4096^3 configuration, outside `value` -----------------------------
+    all_layouts = None
+    if G == 1 and not args.no_layouts:
+        Q = 4096
+        xa = torch.rand(Q * Q, dtype=torch.float32, device=dev) * 2 - 1
+        xb = torch.rand(Q * Q, dtype=torch.float32, device=dev) * 2 - 1
+        xc = torch.empty(Q * Q, dtype=torch.float32, device=dev)
+        fl, rows_l, worst = 2.0 * Q ** 3, {}, None
+        for qa in (0, 1):
+            for qb in (0, 1):
+                for qc in (0, 1):
+                    for _ in range(10):
+                        sg.gemm(qc, qa, qb, xc, xa, xb, Q, Q, Q, stream=stream)
+                    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(30)]
+                    for e0, e1 in evs:
+                        e0.record()
+                        sg.gemm(qc, qa, qb, xc, xa, xb, Q, Q, Q, stream=stream)
+                        e1.record()
+                    torch.cuda.synchronize()
+                    ms = [e0.elapsed_time(e1) for e0, e1 in evs]
+                    launches_total += 40 * (1 + bin(sg.select_config(Q, Q, Q, qc, qa, qb)[0].pretranspose).count("1"))
+                    # a band of rows against a float64 product on the device (relative to max(|ref|, rms(ref)))
+                    a2 = xa.view(Q, Q) if qa == 0 else xa.view(Q, Q).T
+                    b2 = xb.view(Q, Q) if qb == 0 else xb.view(Q, Q).T
+                    c2 = xc.view(Q, Q) if qc == 0 else xc.view(Q, Q).T
+                    ref = a2[:128].double() @ b2.double()
+                    err = ((c2[:128].double() - ref).abs() / torch.maximum(ref.abs(), ref.pow(2).mean().sqrt())).max().item()
+                    avg = fl / (statistics.mean(ms) * 1e-3) / 1e12
+                    rows_l["".join("rc"[x] for x in (qa, qb, qc))] = {
+                        "tflops_avg": avg, "tflops_min_time": fl / (min(ms) * 1e-3) / 1e12,
+                        "pct_of_fp32_peak": 100.0 * avg / peak_nominal, "max_rel_err_vs_f64_128_rows": err}
+                    worst = avg if worst is None else min(worst, avg)
+        all_layouts = {"shape": "4096x4096x4096", "layouts_abc": rows_l, "min_tflops_avg": worst,
+                       "min_pct_of_fp32_peak": 100.0 * worst / peak_nominal,
+                       "tolerance_rel_err": 1e-5 * math.sqrt(Q),
+                       "note": "b200_sgemm per layout (A,B,C), A,B~U[-1,1) generated on the device, 10 warm-ups + 30 "
+                               "launches timed one by one with CUDA events; informational, not part of value"}
+        del xa, xb, xc
+
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": G, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if G > 1 else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -492,7 +574,11 @@ def ours(args, w):
             "launch_ms": {"min": min_ms, "avg": avg_ms, "max": max_ms},
             "identity_bit_exact": check, "allgather_ms": allgather_ms,
             "roofline": roofline, "cpu_baseline": cpu_info, "clocks": clocks, "e2e": e2e,
-            "tf32x3": tf32x3, "fused_gather": fused, "gpu_launches": args.steps * launches_per_step}
+            "tf32x3": tf32x3, "fused_gather": fused, "all_layouts": all_layouts,
+            "single_gpu_same_workload_tflops": single_gpu["tflops"] if single_gpu else None,
+            "single_gpu_same_workload_ms": single_gpu["ms_per_step"] if single_gpu else None,
+            "speedup_vs_single_gpu": value / single_gpu["tflops"] if single_gpu else None,
+            "gpu_launches": args.steps * launches_per_step}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -505,6 +591,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="")
+    ap.add_argument("--no-layouts", action="store_true", help="skip the all-layouts table of the 1-GPU run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     w = parse_workload(args.workload, args.gpus)

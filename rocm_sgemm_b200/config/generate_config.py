@@ -87,7 +87,7 @@ def check_variant(v: tuple) -> str | None:
             return "warp-specialised kernel needs thread tiles of 4 or 8"
         if bm > 256 or bn > 256 or bk > 256:
             return "TMA box dimension over 256"
-        producers = 128 if bs >= 256 else 64
+        producers = 128 if (bs >= 256 and wmc * tm * wnc * tn <= 64) else 64  # ws_producer_threads()
         if bs + producers > 1024:
             return "consumer + producer threads over 1024"
         if (bs + producers) * min_blocks > 2048:

@@ -154,7 +154,9 @@ struct Swizzle
     }
 };
 
-template<int BLOCK_SIZE, int BX, int BK, bool KMAJOR, bool ALIGNED>
+// SWIZZLED = false writes the plain [k][x] tile instead (the warp-specialised kernel's consumers then read every
+// operand the same way; the transposing stores of this fallback route then conflict, which only it pays for).
+template<int BLOCK_SIZE, int BX, int BK, bool KMAJOR, bool ALIGNED, bool SWIZZLED = true>
 struct OperandStager
 {
     // X-contiguous operand: one 16-byte chunk of a k-row per work item.
@@ -267,7 +269,7 @@ struct OperandStager
                 if(EXACT || q < ITEMS)
                 {
                     const int c  = q % L;
-                    const int xs = (4 * (q / L)) ^ Swz::of_chunk(c);
+                    const int xs = SWIZZLED ? (4 * (q / L)) ^ Swz::of_chunk(c) : 4 * (q / L);
                     float*    d  = tile + (4 * c) * BX + xs;
                     const float4 r0 = regs[it][0], r1 = regs[it][1], r2 = regs[it][2], r3 = regs[it][3];
                     *reinterpret_cast<float4*>(d + 0 * BX) = make_float4(r0.x, r1.x, r2.x, r3.x);

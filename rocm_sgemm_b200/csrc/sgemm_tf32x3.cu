@@ -475,6 +475,15 @@ bool encode_kmajor(CUtensorMap* map, const float* base, size_t rows, size_t K, s
     EncodeFn fn = encoder();
     if(!fn)
         return false;
+    // the encoder is a driver call: the device's context must be current in this host thread
+    static thread_local bool context_bound = false;
+    if(!context_bound)
+    {
+        int device = 0;
+        if(cudaGetDevice(&device) == cudaSuccess)
+            cudaSetDevice(device);
+        context_bound = true;
+    }
     const cuuint64_t dims[2]    = {(cuuint64_t)K, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
     const cuuint32_t box[2]     = {(cuuint32_t)T_BK, (cuuint32_t)box_rows};

@@ -11,10 +11,14 @@
 //   * PRODUCER warps fill the ring.  An operand whose M / N extent is contiguous in global memory
 //     (A col-major, B row-major) is fetched by ONE thread with a TMA tile copy (cp.async.bulk.tensor.2d;
 //     out-of-bounds elements are zero-filled by the hardware) that signals the stage's mbarrier by byte
-//     count.  A K-contiguous operand (A row-major, B col-major) is fetched by the producer threads as 4x4
-//     blocks with 128-bit loads, transposed in registers and stored with an XOR swizzle that keeps both
-//     those stores and the consumers' 128-bit reads free of bank conflicts.  Operands that do not meet
-//     TMA's alignment rules fall back to guarded cp.async in the same warps.
+//     count.  A K-contiguous operand (A row-major, B col-major) also arrives by TMA, as a [rows][32 k] box
+//     with the 128-byte swizzle in a small staging ring; the other producer warps move it from there into the
+//     stage's plain [k][x] tile as 4 x 4 blocks (four 128-bit reads, transposition in registers, four 128-bit
+//     writes, both sides conflict-free thanks to the row order the tensor map gives the slot).  The consumers
+//     read every operand the same way, no thread ever waits on global memory and ragged K edges are the
+//     hardware's zero fill.  Operands that do not meet TMA's alignment
+//     rules (or K tiles other than 32) take the older route through registers: 128-bit global loads /
+//     guarded cp.async issued by all four producer warps.
 //   * the CTA is persistent and the producers run ahead into the next piece of work while the consumers store C.
 //     Two schedules (WsArgs::sched):
 //       0  work units (tile, K slice) dealt round-robin: blockIdx.x, +gridDim.x, ...
@@ -41,10 +45,15 @@
 namespace sgemm_b200
 {
 
-// producer warps per CTA: one warpgroup beside 8 or more consumer warps, two warps beside fewer
-__host__ __device__ constexpr int ws_producer_threads(int consumer_threads)
+// Producer threads per CTA: one warpgroup beside 8 or more consumer warps, two warps beside fewer - and two warps
+// beside consumers whose thread tile holds more than 64 accumulators.  Those need about 190 registers; with
+// 256 + 64 threads per CTA the launch bound itself allows 204, so the compiler allocates them directly.  (Handing
+// registers over from a producer warpgroup with setmaxnreg also works, but the code the compiler made for the
+// enlarged budget moved values between registers about ten times per k-step - counted with the profiler's
+// per-opcode instruction counters - and ran at 80 % of the FMA rate where the same loop alone reaches 93 %.)
+__host__ __device__ constexpr int ws_producer_threads(int consumer_threads, int accumulators_per_thread)
 {
-    return consumer_threads >= 256 ? 128 : 64;
+    return (consumer_threads >= 256 && accumulators_per_thread <= 64) ? 128 : 64;
 }
 constexpr int      WS_MAX_EXTRA     = 7; // peers of an 8-GPU node
 constexpr uint32_t WS_SPIN_LIMIT    = 1u << 22;
@@ -59,7 +68,8 @@ struct WsArgs
 {
     GemmArgs g;
     int      total_units;  // tiles * splits
-    int      tma_a, tma_b; // 1: the operand is fetched by TMA through the tensor map below
+    int      tma_a, tma_b; // 1: the operand is fetched by TMA straight into the stage through the tensor map below
+    int      stg_a, stg_b; // 1: K-contiguous operand fetched by TMA into the staging ring and transposed from there
     int*     status;       // device status word
     // Further destinations of the result (same leading dimension as C): the tile is stored to each of them as well.
     // Used to write this GPU's block of C straight into the other GPUs' copies of C through peer mappings, which
@@ -253,15 +263,36 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  : "memory");
 }
 
+// (c0, c1, c2) element coordinates of a three-dimensional map
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
+
 template<class Cfg>
 struct WsLayout
 {
     static constexpr int    STAGE_FLOATS = (Cfg::BM + Cfg::BN) * Cfg::BK;
     static constexpr size_t TILE_BYTES   = size_t(Cfg::STAGES) * STAGE_FLOATS * sizeof(float);
-    // after the tiles: full[STAGES], empty[STAGES] (8 bytes each), abort flag
-    static constexpr size_t SMEM_BYTES = TILE_BYTES + size_t(2 * Cfg::STAGES) * 8 + 16;
-    static constexpr int    PRODUCERS  = ws_producer_threads(Cfg::BLOCK_SIZE);
+    // after the tiles: full[STAGES], empty[STAGES], staging full / empty (8 bytes each), abort flag
+    static constexpr int    PRODUCERS  = ws_producer_threads(Cfg::BLOCK_SIZE, Cfg::TMT * Cfg::TNT);
     static constexpr int    THREADS    = Cfg::BLOCK_SIZE + PRODUCERS;
+    // staging ring of the K-contiguous operands: STG_SLOTS slots of [rows][32 floats] per staged operand behind the
+    // barriers, 1024-byte aligned (the period of TMA's 128-byte swizzle), with their own full / empty barriers
+    static constexpr int    STG_SLOTS  = 2;
+    static constexpr size_t BAR_BYTES  = size_t(2 * Cfg::STAGES + 2 * STG_SLOTS) * 8 + 16;
+    static constexpr bool   CAN_STAGE  = Cfg::BK == 32 && PRODUCERS >= 64;
+    static constexpr size_t stage_slot_bytes(bool a_kmajor, bool b_kmajor)
+    {
+        return (a_kmajor ? size_t(Cfg::BM) * 128 : 0) + (b_kmajor ? size_t(Cfg::BN) * 128 : 0);
+    }
+    // dynamic shared memory of a launch that stages the given operands
+    static constexpr size_t smem_bytes(bool stage_a, bool stage_b)
+    {
+        return TILE_BYTES + BAR_BYTES + ((stage_a || stage_b) ? 1024 + STG_SLOTS * stage_slot_bytes(stage_a, stage_b) : 0);
+    }
     // k-steps unrolled back to back: the whole K tile.  A shallower unroll (compile with -DWS_KU_FORCE=8 or 16)
     // keeps the loop body of the 128-accumulator thread tiles small but measured slower on B200
     // (16x8 tile at 8192^3: 58.3 / 60.1 / 63.3 TFLOP/s for 8 / 16 / 32 steps).
@@ -270,16 +301,136 @@ struct WsLayout
 #else
     static constexpr int    KU = Cfg::BK;
 #endif
-    // Thread tiles of 128 accumulators need more registers than an even split of the register file
-    // gives 8 consumer + 4 producer warps.  Both groups are whole warpgroups then, so the producers hand
-    // registers over (setmaxnreg).  The two budgets add up to exactly what the launch allocated,
-    // 256 x 232 + 128 x 40 = 384 x 168, so the consumers' request can always be met; the host refuses to
-    // launch if the compiled kernel was given fewer than LAUNCH_REGS registers per thread.
-    static constexpr bool REBALANCE_REGS = (Cfg::TMT * Cfg::TNT > 64) && Cfg::BLOCK_SIZE == 256 && Cfg::MIN_BLOCKS == 1;
-    static constexpr int  CONSUMER_REGS  = 232;
-    static constexpr int  PRODUCER_REGS  = 40;
-    static constexpr int  LAUNCH_REGS    = 168;
 };
+
+// One staged operand tile moved into the stage's plain [k][x] tile by NT threads.  The staging slot holds BX rows of
+// 32 k (128 bytes) as TMA wrote them with the 128-byte swizzle (the 16-byte chunk c of slot row r sits at chunk
+// c ^ (r & 7); the slot is 1024-byte aligned), in the row order of the three-dimensional tensor map the host builds:
+// slot row i * (BX / 4) + g holds operand row 4 g + i.  A work item is the 4 x 4 block (rows 4g .. 4g+3, k 4c .. 4c+3):
+// four 128-bit reads, transposition in registers (renaming), four 128-bit writes.  The lanes of a warp take
+// consecutive g: each read instruction touches 32 consecutive slot rows (all eight swizzle positions, 512 bytes in
+// four wavefronts) and each write instruction one contiguous 512-byte piece of a k row: both sides run at the
+// shared-memory pipe's full rate, and a tile costs 16 instructions per 4 KB - every instruction the producers issue is
+// an issue slot the FMA stream of the consumers on the same scheduler does not get.
+template<int NT, int BX, int BK>
+struct StagedTransposer
+{
+    static constexpr int G     = BX / 4;
+    static constexpr int ITEMS = G * (BK / 4);
+    static constexpr int ITERS = (ITEMS + NT - 1) / NT;
+    static_assert(G % 8 == 0, "slot rows i * G + g must keep g's low three bits");
+    // byte offsets of this thread's work items inside a slot / a stage tile: fixed for the whole kernel, so the
+    // per-stage work is one address addition per side and eight memory instructions with immediate offsets
+    int src[ITERS], dst[ITERS];
+    __device__ __forceinline__ void init(int t)
+    {
+#pragma unroll
+        for(int it = 0; it < ITERS; ++it)
+        {
+            const int q = t + it * NT;
+            const int g = q % G, c = q / G;
+            src[it]     = (ITEMS % NT == 0 || q < ITEMS) ? g * 128 + ((c ^ (g & 7)) << 4) : -1;
+            dst[it]     = ((4 * c) * BX + 4 * g) * 4;
+        }
+    }
+    __device__ __forceinline__ void run(const char* slot, float* tile) const
+    {
+#pragma unroll
+        for(int it = 0; it < ITERS; ++it)
+        {
+            if((ITEMS % NT) == 0 || src[it] >= 0)
+            {
+                const char*  sp = slot + src[it];
+                const float4 r0 = *reinterpret_cast<const float4*>(sp + 0 * G * 128);
+                const float4 r1 = *reinterpret_cast<const float4*>(sp + 1 * G * 128);
+                const float4 r2 = *reinterpret_cast<const float4*>(sp + 2 * G * 128);
+                const float4 r3 = *reinterpret_cast<const float4*>(sp + 3 * G * 128);
+                char*        d  = reinterpret_cast<char*>(tile) + dst[it];
+                *reinterpret_cast<float4*>(d + 0 * BX * 4) = make_float4(r0.x, r1.x, r2.x, r3.x);
+                *reinterpret_cast<float4*>(d + 1 * BX * 4) = make_float4(r0.y, r1.y, r2.y, r3.y);
+                *reinterpret_cast<float4*>(d + 2 * BX * 4) = make_float4(r0.z, r1.z, r2.z, r3.z);
+                *reinterpret_cast<float4*>(d + 3 * BX * 4) = make_float4(r0.w, r1.w, r2.w, r3.w);
+            }
+        }
+    }
+};
+
+// (c0, c1, c2) element coordinates of a three-dimensional map
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
+
+template<class Cfg>
+struct WsLayout
+{
+    static constexpr int    STAGE_FLOATS = (Cfg::BM + Cfg::BN) * Cfg::BK;
+    static constexpr size_t TILE_BYTES   = size_t(Cfg::STAGES) * STAGE_FLOATS * sizeof(float);
+    // after the tiles: full[STAGES], empty[STAGES], staging full / empty (8 bytes each), abort flag
+    static constexpr int    PRODUCERS  = ws_producer_threads(Cfg::BLOCK_SIZE, Cfg::TMT * Cfg::TNT);
+    static constexpr int    THREADS    = Cfg::BLOCK_SIZE + PRODUCERS;
+    // staging ring of the K-contiguous operands: STG_SLOTS slots of [rows][32 floats] per staged operand behind the
+    // barriers, 1024-byte aligned (the period of TMA's 128-byte swizzle), with their own full / empty barriers
+    static constexpr int    STG_SLOTS  = 2;
+    static constexpr size_t BAR_BYTES  = size_t(2 * Cfg::STAGES + 2 * STG_SLOTS) * 8 + 16;
+    static constexpr bool   CAN_STAGE  = Cfg::BK == 32 && PRODUCERS >= 64;
+    static constexpr size_t stage_slot_bytes(bool a_kmajor, bool b_kmajor)
+    {
+        return (a_kmajor ? size_t(Cfg::BM) * 128 : 0) + (b_kmajor ? size_t(Cfg::BN) * 128 : 0);
+    }
+    // dynamic shared memory of a launch that stages the given operands
+    static constexpr size_t smem_bytes(bool stage_a, bool stage_b)
+    {
+        return TILE_BYTES + BAR_BYTES + ((stage_a || stage_b) ? 1024 + STG_SLOTS * stage_slot_bytes(stage_a, stage_b) : 0);
+    }
+    // k-steps unrolled back to back: the whole K tile.  A shallower unroll (compile with -DWS_KU_FORCE=8 or 16)
+    // keeps the loop body of the 128-accumulator thread tiles small but measured slower on B200
+    // (16x8 tile at 8192^3: 58.3 / 60.1 / 63.3 TFLOP/s for 8 / 16 / 32 steps).
+#ifdef WS_KU_FORCE
+    static constexpr int    KU = (Cfg::TMT * Cfg::TNT > 64 && Cfg::BK > WS_KU_FORCE) ? WS_KU_FORCE : Cfg::BK;
+#else
+    static constexpr int    KU = Cfg::BK;
+#endif
+};
+
+// One staged operand tile moved into the stage's plain [k][x] tile by NT threads.  The staging slot holds BX rows of
+// 32 k (128 bytes) as TMA wrote them with the 128-byte swizzle (the 16-byte chunk c of slot row r sits at chunk
+// c ^ (r & 7); the slot is 1024-byte aligned), in the row order of the three-dimensional tensor map the host builds:
+// slot row i * (BX / 4) + g holds operand row 4 g + i.  A work item is the 4 x 4 block (rows 4g .. 4g+3, k 4c .. 4c+3):
+// four 128-bit reads, transposition in registers (renaming), four 128-bit writes.  The lanes of a warp take
+// consecutive g: each read instruction touches 32 consecutive slot rows (all eight swizzle positions, 512 bytes in
+// four wavefronts) and each write instruction one contiguous 512-byte piece of a k row: both sides run at the
+// shared-memory pipe's full rate, and a tile costs 16 instructions per 4 KB - every instruction the producers issue is
+// an issue slot the FMA stream of the consumers on the same scheduler does not get.
+template<int NT, int BX, int BK>
+__device__ __forceinline__ void transpose_staged(const char* slot, float* tile, int t)
+{
+    constexpr int G     = BX / 4;
+    constexpr int ITEMS = G * (BK / 4);
+    constexpr int ITERS = (ITEMS + NT - 1) / NT;
+    static_assert(G % 8 == 0, "slot rows i * G + g must keep g's low three bits");
+#pragma unroll
+    for(int it = 0; it < ITERS; ++it)
+    {
+        const int q = t + it * NT;
+        if((ITEMS % NT) == 0 || q < ITEMS)
+        {
+            const int   g = q % G, c = q / G;
+            const char* src = slot + g * 128 + ((c ^ (g & 7)) << 4);
+            const float4 r0 = *reinterpret_cast<const float4*>(src + 0 * G * 128);
+            const float4 r1 = *reinterpret_cast<const float4*>(src + 1 * G * 128);
+            const float4 r2 = *reinterpret_cast<const float4*>(src + 2 * G * 128);
+            const float4 r3 = *reinterpret_cast<const float4*>(src + 3 * G * 128);
+            float*       d  = tile + (4 * c) * BX + 4 * g;
+            *reinterpret_cast<float4*>(d + 0 * BX) = make_float4(r0.x, r1.x, r2.x, r3.x);
+            *reinterpret_cast<float4*>(d + 1 * BX) = make_float4(r0.y, r1.y, r2.y, r3.y);
+            *reinterpret_cast<float4*>(d + 2 * BX) = make_float4(r0.z, r1.z, r2.z, r3.z);
+            *reinterpret_cast<float4*>(d + 3 * BX) = make_float4(r0.w, r1.w, r2.w, r3.w);
+        }
+    }
+}
 
 template<class Cfg, int LA, int LB, int LC, bool ALIGNED>
 __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
@@ -292,8 +443,6 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     constexpr bool A_KMAJOR = (LA == LAYOUT_ROW); // transposed by the producers
     constexpr bool B_KMAJOR = (LB == LAYOUT_COL);
     constexpr int  CONSUMER_WARPS = Cfg::BLOCK_SIZE / 32;
-    using SwzA = Swizzle<BM, BK>;
-    using SwzB = Swizzle<BN, BK>;
     using L    = WsLayout<Cfg>;
     constexpr int KU = L::KU;
     static_assert(MODE == FMA_SCALAR || MODE == FMA_X2_DUP, "warp-specialised kernel: fma_mode 0 or 1");
@@ -306,8 +455,14 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     const uint32_t bar_base = smem_u32(smem) + (uint32_t)L::TILE_BYTES;
     auto           full_bar  = [&](int s) -> uint32_t { return bar_base + 8u * s; };
     auto           empty_bar = [&](int s) -> uint32_t { return bar_base + 8u * (STAGES + s); };
+    auto           sfull_bar  = [&](int j) -> uint32_t { return bar_base + 8u * (2 * STAGES + j); };
+    auto           sempty_bar = [&](int j) -> uint32_t { return bar_base + 8u * (2 * STAGES + L::STG_SLOTS + j); };
     volatile int*  abort_flag = reinterpret_cast<volatile int*>(reinterpret_cast<char*>(smem) + L::TILE_BYTES
-                                                               + 2 * STAGES * 8);
+                                                               + (2 * STAGES + 2 * L::STG_SLOTS) * 8);
+    // the staged route is taken when every operand comes by TMA and at least one of them through the staging ring
+    constexpr bool STAGE_A = L::CAN_STAGE && A_KMAJOR, STAGE_B = L::CAN_STAGE && B_KMAJOR;
+    const bool     staged  = (STAGE_A || STAGE_B) && (w.stg_a || w.stg_b) && (w.tma_a || w.stg_a) && (w.tma_b || w.stg_b);
+    constexpr int  TRANSPOSERS = L::PRODUCERS - 32; // producer warp 0 issues the copies
     auto tile_a = [&](int s) -> float* { return smem + s * L::STAGE_FLOATS; };
     auto tile_b = [&](int s) -> float* { return smem + s * L::STAGE_FLOATS + BM * BK; };
 
@@ -318,8 +473,17 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
         {
             // arrivals per fill: the thread that arms the byte count (and issues the TMA copies), plus one per
             // producer warp when an operand is staged by hand
-            mbar_init(full_bar(s), (w.tma_a && w.tma_b) ? 1 : L::PRODUCERS / 32 + 1);
+            // (staged route: the issuing thread only when an operand goes straight into the stage, plus one per
+            // transposing warp)
+            const uint32_t arrivals = staged ? ((w.tma_a || w.tma_b) ? 1 : 0) + TRANSPOSERS / 32
+                                             : (w.tma_a && w.tma_b) ? 1 : L::PRODUCERS / 32 + 1;
+            mbar_init(full_bar(s), arrivals);
             mbar_init(empty_bar(s), CONSUMER_WARPS);
+        }
+        for(int j = 0; j < L::STG_SLOTS; ++j)
+        {
+            mbar_init(sfull_bar(j), 1);
+            mbar_init(sempty_bar(j), TRANSPOSERS / 32);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -332,12 +496,117 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     if(tid >= Cfg::BLOCK_SIZE)
     {
         // =========================== PRODUCERS ==========================================================
-        if constexpr(L::REBALANCE_REGS)
-            asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(L::PRODUCER_REGS));
         const int      ptid     = tid - Cfg::BLOCK_SIZE;
+        if constexpr(STAGE_A || STAGE_B)
+        {
+            if(staged)
+            {
+                constexpr uint32_t SLOT_A = STAGE_A ? BM * 128u : 0u, SLOT_B = STAGE_B ? BN * 128u : 0u;
+                char* stg = reinterpret_cast<char*>(smem) + L::TILE_BYTES + L::BAR_BYTES;
+                stg += (1024u - (smem_u32(stg) & 1023u)) & 1023u;
+                auto slot_a = [&](int j) -> char* { return stg + j * (SLOT_A + SLOT_B); };
+                auto slot_b = [&](int j) -> char* { return stg + j * (SLOT_A + SLOT_B) + SLOT_A; };
+                const bool stg_a = STAGE_A && w.stg_a, stg_b = STAGE_B && w.stg_b;
+                auto give_up = [&]() {
+                    if(!*abort_flag)
+                    {
+                        *abort_flag = 1;
+                        atomicCAS(w.status, 0, WS_ERR_EMPTY_TIMEOUT);
+                    }
+                    __nanosleep(200000); // let copies already in flight land before the CTA retires
+                };
+                int        s = 0, j = 0;
+                uint32_t   phase = 0, jphase = 0;
+                WsSchedule sch;
+                sch.init(w, tiles, BK);
+                if(ptid >= 32)
+                {
+                    // ---- transposing warps: staging slot -> stage ------------------------------------------------
+                    const int tt = ptid - 32;
+                    StagedTransposer<TRANSPOSERS, BM, BK> tr_a;
+                    StagedTransposer<TRANSPOSERS, BN, BK> tr_b;
+                    tr_a.init(tt);
+                    tr_b.init(tt);
+                    for(int pi = 0; pi < sch.n; ++pi)
+                    {
+                        const WsPiece pc     = sch.piece(pi);
+                        const int     ntiles = (pc.k_end - pc.k_begin + BK - 1) / BK;
+                        for(int t = 0; t < ntiles; ++t)
+                        {
+                            if(!mbar_wait_parked(sfull_bar(j), jphase, abort_flag)
+                               || !mbar_wait_parked(empty_bar(s), phase ^ 1u, abort_flag))
+                            {
+                                give_up();
+                                return;
+                            }
+                            if constexpr(STAGE_A)
+                                if(stg_a)
+                                    tr_a.run(slot_a(j), tile_a(s));
+                            if constexpr(STAGE_B)
+                                if(stg_b)
+                                    tr_b.run(slot_b(j), tile_b(s));
+                            __syncwarp(); // the warp is done with the slot and with the stage: one lane says so
+                            if((ptid & 31) == 0)
+                            {
+                                mbar_arrive(full_bar(s));
+                                mbar_arrive(sempty_bar(j));
+                            }
+                            if(++s == STAGES) { s = 0; phase ^= 1u; }
+                            if(++j == L::STG_SLOTS) { j = 0; jphase ^= 1u; }
+                        }
+                    }
+                    return;
+                }
+                if(ptid != 0)
+                    return;
+                // ---- the issuing thread: every TMA copy of the CTA --------------------------------------------------
+                const uint32_t direct_bytes = (w.tma_a ? BM * BK * 4u : 0u) + (w.tma_b ? BN * BK * 4u : 0u);
+                const uint32_t staged_bytes = (stg_a ? SLOT_A : 0u) + (stg_b ? SLOT_B : 0u);
+                for(int pi = 0; pi < sch.n; ++pi)
+                {
+                    const WsPiece pc = sch.piece(pi);
+                    int           tile_m, tile_n;
+                    map_tile<Cfg::RASTER>(pc.tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
+                    const int m0 = tile_m * BM, n0 = tile_n * BN;
+                    const int ntiles = (pc.k_end - pc.k_begin + BK - 1) / BK;
+                    for(int t = 0; t < ntiles; ++t)
+                    {
+                        const int k0 = pc.k_begin + t * BK;
+                        // the staging slot frees up first (the transposers run ahead of the consumers): fetch into it
+                        // as early as possible; coordinates are (k, row / 4, row % 4), k a multiple of 32 elements
+                        if(!mbar_wait_parked(sempty_bar(j), jphase ^ 1u, abort_flag))
+                        {
+                            give_up();
+                            return;
+                        }
+                        mbar_arrive_expect_tx(sfull_bar(j), staged_bytes);
+                        if(stg_a)
+                            tma_load_3d(smem_u32(slot_a(j)), &map_a, k0, m0 >> 2, 0, sfull_bar(j));
+                        if(stg_b)
+                            tma_load_3d(smem_u32(slot_b(j)), &map_b, k0, n0 >> 2, 0, sfull_bar(j));
+                        if(direct_bytes)
+                        {
+                            if(!mbar_wait_parked(empty_bar(s), phase ^ 1u, abort_flag))
+                            {
+                                give_up();
+                                return;
+                            }
+                            mbar_arrive_expect_tx(full_bar(s), direct_bytes);
+                            if(w.tma_a)
+                                tma_load_2d(smem_u32(tile_a(s)), &map_a, m0, k0, full_bar(s));
+                            if(w.tma_b)
+                                tma_load_2d(smem_u32(tile_b(s)), &map_b, n0, k0, full_bar(s));
+                        }
+                        if(++s == STAGES) { s = 0; phase ^= 1u; }
+                        if(++j == L::STG_SLOTS) { j = 0; jphase ^= 1u; }
+                    }
+                }
+                return;
+            }
+        }
         const uint32_t tx_bytes = (w.tma_a ? BM * BK * 4u : 0u) + (w.tma_b ? BN * BK * 4u : 0u);
-        OperandStager<L::PRODUCERS, BM, BK, A_KMAJOR, ALIGNED> stage_a;
-        OperandStager<L::PRODUCERS, BN, BK, B_KMAJOR, ALIGNED> stage_b;
+        OperandStager<L::PRODUCERS, BM, BK, A_KMAJOR, ALIGNED, false> stage_a;
+        OperandStager<L::PRODUCERS, BN, BK, B_KMAJOR, ALIGNED, false> stage_b;
         const bool manual_a = !w.tma_a, manual_b = !w.tma_b;
         // Both operands by TMA: one thread does everything, the other producer threads leave at once.  (A warp
         // that merely polled a barrier would still take issue slots from the consumers on its scheduler.)
@@ -416,8 +685,6 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     }
 
     // =============================== CONSUMERS ==========================================================
-    if constexpr(L::REBALANCE_REGS)
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(L::CONSUMER_REGS));
     const int warp_id  = tid >> 5;
     const int lane     = tid & 31;
     const int warp_row = warp_id / Cfg::WARPS_N;
@@ -430,18 +697,15 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     float a_frag[2][TMT];
     float b_frag[2][TNT];
 
-    // fragment of k-step `kk` (relative to the pointers passed in) with the swizzle of 16-byte chunk `chunk`
-    auto load_frags = [&](int buf, const float* as, const float* bs, int kk, int chunk) {
-        const int xa = A_KMAJOR ? SwzA::of_chunk(chunk) : 0;
-        const int xb = B_KMAJOR ? SwzB::of_chunk(chunk) : 0;
+    // fragment of k-step `kk` (relative to the pointers passed in); every operand's stage is a plain [k][x] tile
+    auto load_frags = [&](int buf, const float* as, const float* bs, int kk, int /*chunk*/) {
 #pragma unroll
         for(int im = 0; im < Cfg::WM_CNT; ++im)
         {
 #pragma unroll
             for(int v = 0; v < TM / 4; ++v)
             {
-                // the swizzle permutes 16-byte chunks: it applies to each chunk's own index
-                const float4 q = *reinterpret_cast<const float4*>(as + kk * BM + ((tm0 + im * Cfg::SUB_M + 4 * v) ^ xa));
+                const float4 q = *reinterpret_cast<const float4*>(as + kk * BM + (tm0 + im * Cfg::SUB_M + 4 * v));
                 float*       d = &a_frag[buf][im * TM + 4 * v];
                 d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
             }
@@ -452,7 +716,7 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
 #pragma unroll
             for(int v = 0; v < TN / 4; ++v)
             {
-                const float4 q = *reinterpret_cast<const float4*>(bs + kk * BN + ((tn0 + in * Cfg::SUB_N + 4 * v) ^ xb));
+                const float4 q = *reinterpret_cast<const float4*>(bs + kk * BN + (tn0 + in * Cfg::SUB_N + 4 * v));
                 float*       d = &b_frag[buf][in * TN + 4 * v];
                 d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
             }

@@ -57,6 +57,74 @@ def all_gather_c(C_local, layout_c: int, M: int, N: int, world: int, group=None)
     return assemble_c(full, layout_c, M, N, world)
 
 
+def a_upload_slice(layout_a: int, M: int, K: int, world: int, rank: int) -> tuple[int, int]:
+    """(element offset, element count) of the part of the packed replicated A that `rank` uploads from host memory
+    in the host-buffer pipeline: a 1/G-th contiguous range of the buffer (rows for row-major A, columns for col-major
+    A), so that the all-gather of the ranges over NVLink rebuilds the whole of A on every GPU.  M*K must divide."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("bad rank / world size")
+    if (M * K) % world:
+        raise ValueError(f"A ({M}x{K}) does not divide into {world} equal ranges")
+    n = M * K // world
+    return rank * n, n
+
+
+class ShardedHostGemm:
+    """Column-sharded GEMM whose operands and result live in HOST memory, one object per rank.
+
+    Every step each rank uploads 1/G of the replicated A and its own K x N/G slice of B over its own PCIe link,
+    the ranks all-gather A over NVLink (NCCL), each multiplies (sg.gemm: the C ABI's drop-in entry) and downloads
+    its M x N/G block of C.  Host traffic per step is (M*K + K*N + M*N) * 4 bytes for the whole job, whatever G is;
+    uploading all of A on every rank would cost G times the A part.  Two steps are kept in flight on two streams
+    with their own device buffers, so the copies of step i+1 run under the GEMM of step i.
+    """
+
+    def __init__(self, sg, layout_c: int, layout_a: int, layout_b: int, M: int, N: int, K: int, world: int, rank: int,
+                 group=None):
+        import torch
+        self.sg, self.lc, self.la, self.lb = sg, layout_c, layout_a, layout_b
+        self.M, self.N, self.K, self.world, self.rank, self.group = M, N, K, world, rank, group
+        _, self.n = shard_columns(N, world, rank)
+        self.a_off, self.a_len = a_upload_slice(layout_a, M, K, world, rank)
+        self.slots = []
+        for _ in range(2):
+            self.slots.append({
+                "stream": torch.cuda.Stream(),
+                "A": torch.empty(M * K, dtype=torch.float32, device="cuda"),
+                "B": torch.empty(K * self.n, dtype=torch.float32, device="cuda"),
+                "C": torch.empty(M * self.n, dtype=torch.float32, device="cuda"),
+                "done": None})
+        self.h2d_bytes = (self.a_len + K * self.n) * 4
+        self.d2h_bytes = M * self.n * 4
+        self.step = 0
+
+    def submit(self, hC_local, hA, hB_local):
+        """Enqueues one step (pinned host tensors: the whole A, this rank's B slice, this rank's C block)."""
+        import torch
+        import torch.distributed as dist
+        slot = self.slots[self.step % 2]
+        self.step += 1
+        if slot["done"] is not None:
+            slot["done"].synchronize()  # the step that used these buffers two submits ago
+        with torch.cuda.stream(slot["stream"]):
+            mine = slot["A"][self.a_off:self.a_off + self.a_len]
+            mine.copy_(hA[self.a_off:self.a_off + self.a_len], non_blocking=True)
+            slot["B"].copy_(hB_local, non_blocking=True)
+            if self.world > 1:
+                dist.all_gather_into_tensor(slot["A"], mine, group=self.group)
+            self.sg.gemm(self.lc, self.la, self.lb, slot["C"], slot["A"], slot["B"], self.M, self.n, self.K,
+                         stream=slot["stream"])
+            hC_local.copy_(slot["C"], non_blocking=True)
+            slot["done"] = torch.cuda.Event()
+            slot["done"].record(slot["stream"])
+        return slot["done"]
+
+    def wait_all(self):
+        for slot in self.slots:
+            if slot["done"] is not None:
+                slot["done"].synchronize()
+
+
 def block_offset(layout_c: int, M: int, N: int, world: int, rank: int) -> tuple[int, int]:
     """(element offset of rank's column block inside a full packed M x N matrix, leading dimension of that matrix).
     Row-major C: the block starts at column rank*N/G of row 0, rows are N apart.  Col-major C: the block is the
