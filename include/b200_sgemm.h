@@ -67,9 +67,11 @@ int b200_sgemm(int layout_c, int layout_a, int layout_b, float* C, const float* 
 
 /* Same operation with everything the drop-in entry decides made explicit: leading dimensions in
  * elements (0 = packed), a forced kernel variant (-1 = look up the table, as
- * detail::find_best_config does in rocm_sgemm/src/gemm.cpp:12), a forced split-K (0 = the table's)
- * and a caller-owned workspace for the split-K partial sums (may be NULL when the effective split
- * is 1; otherwise at least b200_sgemm_workspace_bytes()).  The tuner drives kernels through this
+ * detail::find_best_config does in rocm_sgemm/src/gemm.cpp:12), a forced split-K (0 = the table's when the
+ * variant is looked up, no split with a forced variant; n >= 2 = n equal K slices summed in order by a second
+ * kernel; -1 = equal K ranges per CTA summed in order inside the kernel, for problems with fewer tiles than SMs)
+ * and a caller-owned workspace (required for n >= 2 slices: at least b200_sgemm_workspace_bytes(); optional
+ * otherwise, see there).  The tuner drives kernels through this
  * entry the way the reference's tuner launches a JIT-compiled instantiation directly
  * (rocm_sgemm/config/tuner.cpp:419-429); the column-sharded multi-GPU driver uses the leading
  * dimensions. */
@@ -91,7 +93,21 @@ int b200_sgemm_multi(int layout_c, int layout_a, int layout_b, float* const* C_l
                      const float* B, size_t M, size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant,
                      void* cuda_stream);
 
-/* Bytes of split-K workspace b200_sgemm_ex needs for this call (0 when the effective split is 1). */
+/* The K cut points of the "equal ranges" schedule (split_k -1 in b200_sgemm_ex, split_k 0 in a table entry) for
+ * a problem on a device with sm_count SMs, so that a host-side check can restate the arithmetic: every tile's K
+ * extent is cut at the reported points, each piece is a k-ascending FMA chain from zero, and C is the sum of the
+ * pieces in ascending K order.  Tiles are block_mnk[0] x block_mnk[1] (block_mnk[2] = the K tile), numbered
+ * tile_row * ceil(N / block_n) + tile_column; offsets[t] .. offsets[t+1] index tile t's cut points in `bounds` (K
+ * positions strictly between 0 and K).  Returns the total number of cut points (0 = this call would not use the
+ * schedule: no cuts at all, or equal slices), negative = error; at most `capacity` entries of either array are
+ * written (offsets needs tiles + 1).  No reference counterpart: the reference's kernel never splits K. */
+int b200_sgemm_stream_plan(int layout_c, int layout_a, int layout_b, size_t M, size_t N, size_t K, int variant,
+                           int split_k, int sm_count, int* block_mnk, int* offsets, int* bounds, int capacity);
+
+/* Bytes of workspace b200_sgemm_ex can use for this call: the split-K partial sums when the effective split is
+ * > 1 (required), else the accumulator parking slots of the balanced schedules on the current device (optional:
+ * with a smaller or no workspace the call runs the plain schedule and, unless split_k is -1, computes the same
+ * bits), else 0. */
 size_t b200_sgemm_workspace_bytes(int layout_c, int layout_a, int layout_b, size_t M, size_t N, size_t K, int variant,
                                   int split_k);
 

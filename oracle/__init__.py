@@ -44,6 +44,9 @@ def _load():
     lib.oracle_sgemm_f32.argtypes = [ctypes.c_int] * 3 + [_fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz, ctypes.c_int]
     lib.oracle_sgemm_fma.argtypes = [ctypes.c_int] * 3 + [_fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz, ctypes.c_int, _sz,
                                                            ctypes.c_int]
+    lib.oracle_sgemm_fma_pieces.argtypes = [ctypes.c_int] * 3 + [_fp, _fp, _fp, _sz, _sz, _sz, _sz, _sz, _sz, _sz,
+                                                                  ctypes.POINTER(ctypes.c_int),
+                                                                  ctypes.POINTER(ctypes.c_int), ctypes.c_int]
     lib.oracle_sgemm_f64.argtypes = [ctypes.c_int] * 3 + [_dp, _fp, _fp, _sz, _sz, _sz, _sz, _sz, ctypes.c_int]
     lib.oracle_error_metrics.argtypes = [ctypes.c_int, _fp, _dp, _sz, _sz, _sz, _sz, _dp]
     lib.oracle_max_threads.restype = ctypes.c_int
@@ -120,6 +123,19 @@ def sgemm_fma(lc, la, lb, A, B, M, N, K, rows=None, splits=1, k_align=1, threads
     C = np.zeros(M * N, dtype=np.float32)
     r0, r1 = _band(M, rows)
     lib().oracle_sgemm_fma(lc, la, lb, _f(C), _f(A), _f(B), M, N, K, r0, r1, splits, k_align, threads)
+    return C
+
+
+def sgemm_fma_pieces(lc, la, lb, A, B, M, N, K, block_m, block_n, offsets, bounds, rows=None, threads=1) -> np.ndarray:
+    """FMA chains with per-tile K cut points, added in ascending K order (offsets / bounds as returned by the
+    library's stream_plan: offsets has tiles + 1 entries, tile = tile_row * ceil(N / block_n) + tile_column)."""
+    C = np.zeros(M * N, dtype=np.float32)
+    r0, r1 = _band(M, rows)
+    offs = np.ascontiguousarray(offsets, dtype=np.int32)
+    bnd = np.ascontiguousarray(bounds if len(bounds) else [0], dtype=np.int32)
+    ip = ctypes.POINTER(ctypes.c_int)
+    lib().oracle_sgemm_fma_pieces(lc, la, lb, _f(C), _f(A), _f(B), M, N, K, r0, r1, block_m, block_n,
+                                  offs.ctypes.data_as(ip), bnd.ctypes.data_as(ip), threads)
     return C
 
 

@@ -204,6 +204,41 @@ void oracle_sgemm_fma(int lc, int la, int lb, float* C, const float* A, const fl
     }
 }
 
+/* The same chains with tile-dependent K cut points (the schedule that cuts the tiles' K extents into equal ranges
+ * per CTA): C(i,j) belongs to tile (i / block_m) * ceil(N / block_n) + j / block_n, whose cut points are
+ * bounds[offsets[t] .. offsets[t+1]) (ascending, strictly between 0 and K).  Every piece is a k-ascending fmaf chain
+ * from zero and the pieces are added in ascending K order: total = ((p0 + p1) + p2) + ...
+ * (The reference's kernel, kernel/kernel.hpp:188-266, is the single-piece case.) */
+void oracle_sgemm_fma_pieces(int lc, int la, int lb, float* C, const float* A, const float* B, size_t M, size_t N,
+                             size_t K, size_t row_begin, size_t row_end, size_t block_m, size_t block_n,
+                             const int* offsets, const int* bounds, int threads)
+{
+    const size_t grid_n = (N + block_n - 1) / block_n;
+#ifdef _OPENMP
+#pragma omp parallel for num_threads(threads > 0 ? threads : 1) schedule(static)
+#endif
+    for(size_t i = row_begin; i < row_end; ++i)
+    {
+        for(size_t j = 0; j < N; ++j)
+        {
+            const size_t t     = (i / block_m) * grid_n + j / block_n;
+            const int    first = offsets[t], last = offsets[t + 1];
+            float        total = 0.0f;
+            size_t       k0    = 0;
+            for(int piece = first; piece <= last; ++piece)
+            {
+                const size_t k1  = piece < last ? (size_t)bounds[piece] : K;
+                float        acc = 0.0f;
+                for(size_t k = k0; k < k1; ++k)
+                    acc = fmaf(A[idx(la, M, K, i, k)], B[idx(lb, K, N, k, j)], acc);
+                total = (piece == first) ? acc : total + acc;
+                k0    = k1;
+            }
+            C[idx(lc, M, N, i, j)] = total;
+        }
+    }
+}
+
 /* float64 accumulation of the exact float products; the yardstick for the error bound
  * 1e-5*sqrt(K).  Output stays in double. */
 void oracle_sgemm_f64(int lc, int la, int lb, double* C, const float* A, const float* B, size_t M, size_t N, size_t K,

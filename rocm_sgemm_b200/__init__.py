@@ -89,7 +89,7 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
            "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
-           "b200_sgemm_blas_shutdown", "b200_sgemm_multi")
+           "b200_sgemm_blas_shutdown", "b200_sgemm_multi", "b200_sgemm_stream_plan")
 
 
 def lib() -> ctypes.CDLL:
@@ -123,6 +123,8 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_multi.argtypes = [i, i, i, ctypes.POINTER(_vp), i, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_strided_batched.argtypes =[i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _vp]
     l.b200_sgemm_blas.argtypes = [i, i, _sz, _sz, _sz, ctypes.c_float, _vp, _sz, _vp, _sz, ctypes.c_float, _vp, _sz, _vp]
+    ip = ctypes.POINTER(i)
+    l.b200_sgemm_stream_plan.argtypes = [i, i, i, _sz, _sz, _sz, i, i, i, ip, ip, ip, i]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
     _lib = l
@@ -251,6 +253,26 @@ def host_plan(M: int, N: int, K: int, sm_count: int = 148) -> list:
 def gemm_host_wait(ticket: int) -> None:
     """Blocks until the job behind `ticket` has its C complete in host memory."""
     _check(lib().b200_sgemm_host_wait(int(ticket)))
+
+
+def stream_plan(layout_c, layout_a, layout_b, M: int, N: int, K: int, variant: int = -1, split_k: int = 0,
+                sm_count: int = 148):
+    """K cut points of the equal-ranges schedule: ((block_m, block_n, block_k), offsets, bounds) with numpy int32
+    arrays (offsets has tiles + 1 entries), or ((block_m, block_n, block_k), None, None) when the call would not use it."""
+    import numpy as np
+    blk = (ctypes.c_int * 3)()
+    n = lib().b200_sgemm_stream_plan(int(layout_c), int(layout_a), int(layout_b), M, N, K, variant, split_k, sm_count,
+                                     blk, None, None, 0)
+    if n < 0:
+        raise SgemmError(n, status_string(n))
+    if n == 0:
+        return tuple(blk), None, None
+    tiles = -(-M // blk[0]) * -(-N // blk[1])
+    cap = max(tiles + 1, n)
+    offs, bnd = (ctypes.c_int * cap)(), (ctypes.c_int * cap)()
+    lib().b200_sgemm_stream_plan(int(layout_c), int(layout_a), int(layout_b), M, N, K, variant, split_k, sm_count, blk,
+                                 offs, bnd, cap)
+    return tuple(blk), np.array(offs[:tiles + 1], dtype=np.int32), np.array(bnd[:n], dtype=np.int32)
 
 
 def workspace_bytes(layout_c, layout_a, layout_b, M, N, K, variant: int = -1, split_k: int = 0) -> int:

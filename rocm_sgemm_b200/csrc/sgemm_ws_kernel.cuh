@@ -30,6 +30,11 @@
 //          kernel.  Every C element is therefore still ONE k-ascending FMA chain (bit-identical to schedule 0
 //          without split-K); the chain merely changes hands once.  Needs ranges of at least one whole tile
 //          (tiles >= CTAs), so that no tile is shared by more than two CTAs.
+//       2  the same equal ranges when there are FEWER tiles than CTAs (small or skinny problems): a tile is then shared
+//          by several CTAs, each of which runs its K range as a chain of its own starting from zero.  All but the last
+//          range of a tile are parked; the CTA that owns the last range waits for them and adds them up in ascending
+//          K order (then its own), so the result is the deterministic ordered sum of chains - the arithmetic of
+//          split-K with tile-dependent cut points, which ws_stream_bounds() reports to the host.
 //
 // Packed FMA: the B fragment supplies natural pairs of neighbouring columns (64-bit halves of the
 // 128-bit shared-memory read), the A value is duplicated into both halves.  The FMA order keeps the pair
@@ -76,7 +81,7 @@ struct WsArgs
     // folds the all-gather that follows a column-sharded product into the epilogue.  Only without split-K.
     int      n_extra;
     float*   extra_c[WS_MAX_EXTRA];
-    // schedule 1 (see the head of this file)
+    // schedules 1 and 2 (see the head of this file)
     int       sched;
     int       k_tiles;  // K tiles per tile: ceil(K / block_k)
     float*    handover; // gridDim.x slots of block_m x block_n floats: slot c holds what CTA c parked
@@ -89,17 +94,29 @@ struct WsPiece
 {
     int tile_id;
     int k_begin, k_end;
-    int split; // schedule 0: index of the K slice (selects the partial-sum matrix)
-    int recv;  // >= 0: start from the accumulators parked in this slot instead of zero
-    int send;  // >= 0: park the accumulators in this slot instead of storing C
+    int split;  // schedule 0: index of the K slice (selects the partial-sum matrix)
+    int recv;   // schedule 1, >= 0: start from the accumulators parked in this slot instead of zero
+    int send;   // >= 0: park the accumulators in this slot instead of storing C
+    int reduce; // schedule 2, >= 0: before storing C add the parked accumulators of slots reduce .. blockIdx.x-1
 };
+
+// First unit (K tile of the tile sequence) of CTA c when `units` units are cut into `ctas` equal ranges.
+__host__ __device__ inline long long ws_range_begin(long long units, int ctas, int c)
+{
+    return units * c / ctas;
+}
 
 // The list of pieces of this CTA, identical for its producer and consumer threads.
 struct WsSchedule
 {
     int n;
-    int sched, tiles, stride, first;              // schedule 0
-    int head_tile, head_kt, whole0, tail_kt, kts; // schedule 1
+    int sched, tiles, stride, first; // schedule 0
+    // schedules 1 and 2: the range is [tail of a tile][whole tiles][head of a tile]; the head (or a piece from the
+    // middle of a tile) is parked and comes first, the tail continues / gathers and comes last
+    int park_tile, park_a, park_b; // parked piece: K tiles [park_a, park_b) of park_tile, park_tile < 0: none
+    int last_tile, last_a;         // tail piece: K tiles [last_a, kts) of last_tile, last_tile < 0: none
+    int last_first;                // schedule 2: the CTA that owns the first piece of last_tile
+    int whole0, nwhole, kts;
     int bk, K, k_per_split;
 
     __device__ __forceinline__ void init(const WsArgs& w, int tiles_, int BK)
@@ -114,25 +131,47 @@ struct WsSchedule
             first  = blockIdx.x;
             stride = gridDim.x;
             n      = first < w.total_units ? (w.total_units - first + stride - 1) / stride : 0;
+            return;
         }
-        else
+        kts = w.k_tiles;
+        const long long units = (long long)tiles * kts;
+        const long long u0    = ws_range_begin(units, gridDim.x, blockIdx.x);
+        const long long u1    = ws_range_begin(units, gridDim.x, blockIdx.x + 1);
+        park_tile = last_tile = -1;
+        park_a = park_b = last_a = last_first = 0;
+        whole0 = nwhole = 0;
+        if(u1 > u0)
         {
-            kts = w.k_tiles;
-            const long long units = (long long)tiles * kts;
-            const long long u0    = units * blockIdx.x / gridDim.x;
-            const long long u1    = units * (blockIdx.x + 1) / gridDim.x;
-            const int       x     = (int)(u0 / kts);
-            tail_kt               = (int)(u0 - (long long)x * kts); // > 0: the range starts inside tile x
-            head_tile             = (int)(u1 / kts);
-            head_kt               = (int)(u1 - (long long)head_tile * kts); // > 0: the range ends inside head_tile
-            whole0                = tail_kt > 0 ? x + 1 : x;
-            n                     = (head_kt > 0 ? 1 : 0) + (head_tile - whole0) + (tail_kt > 0 ? 1 : 0);
+            const int x = (int)(u0 / kts), a = (int)(u0 - (long long)x * kts);       // first segment: tile x from a
+            const int y = (int)((u1 - 1) / kts), b = (int)(u1 - (long long)y * kts); // last segment: tile y up to b
+            if(x == y)
+            {
+                if(a == 0 && b == kts) { whole0 = x; nwhole = 1; }
+                else if(b == kts) { last_tile = x; last_a = a; }
+                else { park_tile = x; park_a = a; park_b = b; }
+            }
+            else
+            {
+                whole0 = a == 0 ? x : x + 1;
+                nwhole = (b == kts ? y + 1 : y) - whole0;
+                if(a > 0) { last_tile = x; last_a = a; }
+                if(b < kts) { park_tile = y; park_a = 0; park_b = b; }
+            }
+            if(last_tile >= 0 && sched == 2)
+            {
+                // the owner of the first K tile of last_tile: walk down from the neighbour
+                int c = blockIdx.x - 1;
+                while(c > 0 && ws_range_begin(units, gridDim.x, c) > (long long)last_tile * kts)
+                    --c;
+                last_first = c;
+            }
         }
+        n = (park_tile >= 0 ? 1 : 0) + nwhole + (last_tile >= 0 ? 1 : 0);
     }
     __device__ __forceinline__ WsPiece piece(int i) const
     {
         WsPiece p;
-        p.recv = p.send = -1;
+        p.recv = p.send = p.reduce = -1;
         p.split = 0;
         if(sched == 0)
         {
@@ -143,15 +182,15 @@ struct WsSchedule
             p.k_end        = min(K, p.k_begin + k_per_split);
             return p;
         }
-        const int h = head_kt > 0 ? 1 : 0;
+        const int h = park_tile >= 0 ? 1 : 0;
         if(h && i == 0)
         {
-            p.tile_id = head_tile; // first of all: the head of the last tile, parked for the next CTA
-            p.k_begin = 0;
-            p.k_end   = head_kt * bk; // < K: a head never reaches the last K tile
+            p.tile_id = park_tile; // first of all: the piece somebody else waits for
+            p.k_begin = park_a * bk;
+            p.k_end   = park_b * bk; // < K: a parked piece never reaches the last K tile
             p.send    = blockIdx.x;
         }
-        else if(i - h < head_tile - whole0)
+        else if(i - h < nwhole)
         {
             p.tile_id = whole0 + (i - h);
             p.k_begin = 0;
@@ -159,14 +198,42 @@ struct WsSchedule
         }
         else
         {
-            p.tile_id = whole0 - 1; // last of all: the tail of the first tile, continued from the previous CTA
-            p.k_begin = tail_kt * bk;
+            p.tile_id = last_tile; // last of all: the tail of the first tile
+            p.k_begin = last_a * bk;
             p.k_end   = K;
-            p.recv    = blockIdx.x - 1;
+            if(sched == 1)
+                p.recv = blockIdx.x - 1; // continue the neighbour's chain
+            else
+                p.reduce = last_first;   // own chain, then the ordered sum of the earlier pieces
         }
         return p;
     }
 };
+
+// Host-side view of schedule 2: the K cut points of the tile at position `pos` of the tile order, in K tiles:
+// writes the cut points strictly inside (0, kts) in ascending order and returns how many there are.
+inline int ws_stream_cuts(long long tiles, int kts, int ctas, long long pos, int* cuts, int capacity)
+{
+    const long long units = tiles * kts;
+    int             n     = 0;
+    // CTAs whose range begins inside this tile
+    long long c = (pos * kts * ctas) / units; // a CTA at or before the first candidate
+    while(c > 0 && ws_range_begin(units, ctas, (int)c) > pos * kts)
+        --c;
+    for(; c <= ctas; ++c)
+    {
+        const long long u = ws_range_begin(units, ctas, (int)c);
+        if(u >= (pos + 1) * kts)
+            break;
+        if(u > pos * kts)
+        {
+            if(n < capacity)
+                cuts[n] = (int)(u - pos * kts);
+            ++n;
+        }
+    }
+    return n;
+}
 
 // ---- mbarrier / TMA helpers ------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
@@ -354,83 +421,6 @@ struct StagedTransposer
         }
     }
 };
-
-// (c0, c1, c2) element coordinates of a three-dimensional map
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-                 : "memory");
-}
-
-template<class Cfg>
-struct WsLayout
-{
-    static constexpr int    STAGE_FLOATS = (Cfg::BM + Cfg::BN) * Cfg::BK;
-    static constexpr size_t TILE_BYTES   = size_t(Cfg::STAGES) * STAGE_FLOATS * sizeof(float);
-    // after the tiles: full[STAGES], empty[STAGES], staging full / empty (8 bytes each), abort flag
-    static constexpr int    PRODUCERS  = ws_producer_threads(Cfg::BLOCK_SIZE, Cfg::TMT * Cfg::TNT);
-    static constexpr int    THREADS    = Cfg::BLOCK_SIZE + PRODUCERS;
-    // staging ring of the K-contiguous operands: STG_SLOTS slots of [rows][32 floats] per staged operand behind the
-    // barriers, 1024-byte aligned (the period of TMA's 128-byte swizzle), with their own full / empty barriers
-    static constexpr int    STG_SLOTS  = 2;
-    static constexpr size_t BAR_BYTES  = size_t(2 * Cfg::STAGES + 2 * STG_SLOTS) * 8 + 16;
-    static constexpr bool   CAN_STAGE  = Cfg::BK == 32 && PRODUCERS >= 64;
-    static constexpr size_t stage_slot_bytes(bool a_kmajor, bool b_kmajor)
-    {
-        return (a_kmajor ? size_t(Cfg::BM) * 128 : 0) + (b_kmajor ? size_t(Cfg::BN) * 128 : 0);
-    }
-    // dynamic shared memory of a launch that stages the given operands
-    static constexpr size_t smem_bytes(bool stage_a, bool stage_b)
-    {
-        return TILE_BYTES + BAR_BYTES + ((stage_a || stage_b) ? 1024 + STG_SLOTS * stage_slot_bytes(stage_a, stage_b) : 0);
-    }
-    // k-steps unrolled back to back: the whole K tile.  A shallower unroll (compile with -DWS_KU_FORCE=8 or 16)
-    // keeps the loop body of the 128-accumulator thread tiles small but measured slower on B200
-    // (16x8 tile at 8192^3: 58.3 / 60.1 / 63.3 TFLOP/s for 8 / 16 / 32 steps).
-#ifdef WS_KU_FORCE
-    static constexpr int    KU = (Cfg::TMT * Cfg::TNT > 64 && Cfg::BK > WS_KU_FORCE) ? WS_KU_FORCE : Cfg::BK;
-#else
-    static constexpr int    KU = Cfg::BK;
-#endif
-};
-
-// One staged operand tile moved into the stage's plain [k][x] tile by NT threads.  The staging slot holds BX rows of
-// 32 k (128 bytes) as TMA wrote them with the 128-byte swizzle (the 16-byte chunk c of slot row r sits at chunk
-// c ^ (r & 7); the slot is 1024-byte aligned), in the row order of the three-dimensional tensor map the host builds:
-// slot row i * (BX / 4) + g holds operand row 4 g + i.  A work item is the 4 x 4 block (rows 4g .. 4g+3, k 4c .. 4c+3):
-// four 128-bit reads, transposition in registers (renaming), four 128-bit writes.  The lanes of a warp take
-// consecutive g: each read instruction touches 32 consecutive slot rows (all eight swizzle positions, 512 bytes in
-// four wavefronts) and each write instruction one contiguous 512-byte piece of a k row: both sides run at the
-// shared-memory pipe's full rate, and a tile costs 16 instructions per 4 KB - every instruction the producers issue is
-// an issue slot the FMA stream of the consumers on the same scheduler does not get.
-template<int NT, int BX, int BK>
-__device__ __forceinline__ void transpose_staged(const char* slot, float* tile, int t)
-{
-    constexpr int G     = BX / 4;
-    constexpr int ITEMS = G * (BK / 4);
-    constexpr int ITERS = (ITEMS + NT - 1) / NT;
-    static_assert(G % 8 == 0, "slot rows i * G + g must keep g's low three bits");
-#pragma unroll
-    for(int it = 0; it < ITERS; ++it)
-    {
-        const int q = t + it * NT;
-        if((ITEMS % NT) == 0 || q < ITEMS)
-        {
-            const int   g = q % G, c = q / G;
-            const char* src = slot + g * 128 + ((c ^ (g & 7)) << 4);
-            const float4 r0 = *reinterpret_cast<const float4*>(src + 0 * G * 128);
-            const float4 r1 = *reinterpret_cast<const float4*>(src + 1 * G * 128);
-            const float4 r2 = *reinterpret_cast<const float4*>(src + 2 * G * 128);
-            const float4 r3 = *reinterpret_cast<const float4*>(src + 3 * G * 128);
-            float*       d  = tile + (4 * c) * BX + 4 * g;
-            *reinterpret_cast<float4*>(d + 0 * BX) = make_float4(r0.x, r1.x, r2.x, r3.x);
-            *reinterpret_cast<float4*>(d + 1 * BX) = make_float4(r0.y, r1.y, r2.y, r3.y);
-            *reinterpret_cast<float4*>(d + 2 * BX) = make_float4(r0.z, r1.z, r2.z, r3.z);
-            *reinterpret_cast<float4*>(d + 3 * BX) = make_float4(r0.w, r1.w, r2.w, r3.w);
-        }
-    }
-}
 
 template<class Cfg, int LA, int LB, int LC, bool ALIGNED>
 __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
@@ -948,6 +938,57 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                 st_release_u32(w.flags + pc.send * CONSUMER_WARPS + warp_id, w.epoch);
             }
             continue;
+        }
+        if(pc.reduce >= 0)
+        {
+            // schedule 2: this CTA owns the last K range of the tile.  Total = ((p_first + p_next) + ...) + own, in
+            // ascending K order; each earlier piece was parked by its CTA before that CTA did anything else.
+            float sum[TMT][TNT];
+            for(int src_cta = pc.reduce; src_cta < (int)blockIdx.x; ++src_cta)
+            {
+                const unsigned* flag = w.flags + src_cta * CONSUMER_WARPS + warp_id;
+                bool            got  = ld_acquire_u32(flag) == w.epoch;
+                if(!got)
+                {
+                    const uint64_t t0 = global_timer_ns();
+                    for(uint32_t it = 0; it < WS_SPIN_LIMIT && !got; ++it)
+                    {
+                        __nanosleep(100);
+                        got = ld_acquire_u32(flag) == w.epoch;
+                        if(!got && (it & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > WS_WAIT_LIMIT_NS))
+                            break;
+                    }
+                }
+                if(!got)
+                {
+                    if(!*abort_flag)
+                    {
+                        *abort_flag = 1;
+                        atomicCAS(w.status, 0, WS_ERR_PEER_TIMEOUT);
+                    }
+                    return;
+                }
+                const float4* src = reinterpret_cast<const float4*>(w.handover + (size_t)src_cta * (BM * BN)) + tid;
+#pragma unroll
+                for(int v = 0; v < ACC_VEC; ++v)
+                {
+                    const float4 q = __ldcg(src + v * Cfg::BLOCK_SIZE);
+                    float*       d = &sum[0][0] + 4 * v;
+                    if(src_cta == pc.reduce)
+                    {
+                        d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
+                    }
+                    else
+                    {
+                        d[0] += q.x; d[1] += q.y; d[2] += q.z; d[3] += q.w;
+                    }
+                }
+            }
+#pragma unroll
+            for(int i = 0; i < TMT; ++i)
+#pragma unroll
+                for(int j = 0; j < TNT; ++j)
+                    c[i][j] = sum[i][j] + c[i][j];
         }
         store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)pc.split * p.split_stride, m0 + tm0, n0 + tn0);
         for(int d = 0; d < w.n_extra; ++d) // plain stores; to a peer GPU's memory when the pointer is a peer mapping

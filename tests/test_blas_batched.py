@@ -17,8 +17,9 @@ def dev(a):
 
 def chain(sgemm, orc, lc, la, lb, A, B, M, N, K):
     """The oracle's result with the split the table selects for this problem."""
-    p, _ = sgemm.select_config(M, N, K, lc, la, lb)
-    return orc.sgemm_fma(lc, la, lb, A, B, M, N, K, splits=p.split_k, k_align=p.block_k, threads=orc.max_threads())
+    from common import oracle_chain
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return oracle_chain(sgemm, orc, la, lb, lc, A, B, M, N, K, sms)
 
 
 @pytest.mark.parametrize("layout", [(0, 0, 0), (1, 0, 1), (0, 1, 0), (1, 1, 1)], ids=lambda l: layout_name(*l))

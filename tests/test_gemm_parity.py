@@ -15,7 +15,7 @@ import math
 import numpy as np
 import pytest
 
-from common import LAYOUTS, REFERENCE_TEST_SHAPES, SWEEP_SHAPES, as2d, bits, layout_name
+from common import LAYOUTS, REFERENCE_TEST_SHAPES, SWEEP_SHAPES, as2d, bits, layout_name, oracle_chain
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -50,9 +50,13 @@ def effective_split(sgemm, la, lb, lc, M, N, K, variant=-1, split_k=0):
     return s, p.block_k
 
 
+def sm_count():
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
 def expect_bit_exact(sgemm, orc, la, lb, lc, A, B, M, N, K, C, rows=None, **ex):
-    s, bk = effective_split(sgemm, la, lb, lc, M, N, K, ex.get("variant", -1), ex.get("split_k", 0))
-    want = orc.sgemm_fma(lc, la, lb, A, B, M, N, K, rows=rows, splits=s, k_align=bk, threads=orc.max_threads())
+    want = oracle_chain(sgemm, orc, la, lb, lc, A, B, M, N, K, sm_count(), rows, ex.get("variant", -1),
+                        ex.get("split_k", 0))
     got, want2 = as2d(C, lc, M, N), as2d(want, lc, M, N)
     if rows is not None:
         got, want2 = got[rows[0]:rows[1]], want2[rows[0]:rows[1]]

@@ -101,3 +101,34 @@ def test_identity_and_pattern_fills(orc):
     A, _ = orc.fill_ab(1, 0, 0, 5, 5, 5, with_b=False)
     C = orc.sgemm_fma(0, 0, 0, A, orc.fill_identity(0, 5, 5), 5, 5, 5)
     assert np.array_equal(bits(C), bits(A))
+
+
+def test_fma_pieces_restates_ordered_sum_of_chains(orc):
+    """Per-tile K cut points: with the same cut points in every tile the result is the split-K restatement, with no
+    cut points the single chain; a tile with its own cut points differs from its neighbours only inside that tile."""
+    M, N, K, bm, bn = 96, 80, 100, 32, 32
+    A, B = orc.fill_ab(7, 0, 1, M, N, K)
+    tiles = 3 * 3
+    none = orc.sgemm_fma_pieces(0, 0, 1, A, B, M, N, K, bm, bn, np.zeros(tiles + 1, np.int32), np.zeros(0, np.int32))
+    assert np.array_equal(none.view(np.uint32), orc.sgemm_fma(0, 0, 1, A, B, M, N, K).view(np.uint32))
+    # slices of 48 in every tile = sgemm_fma(splits=3, k_align=16): [0,48) [48,96) [96,100)
+    offs = np.arange(tiles + 1, dtype=np.int32) * 2
+    bnd = np.tile(np.array([48, 96], np.int32), tiles)
+    same = orc.sgemm_fma_pieces(0, 0, 1, A, B, M, N, K, bm, bn, offs, bnd)
+    assert np.array_equal(same.view(np.uint32), orc.sgemm_fma(0, 0, 1, A, B, M, N, K, splits=3, k_align=16).view(np.uint32))
+    # only tile (1, 2) is cut, at k = 40: checked against a direct evaluation
+    offs = np.zeros(tiles + 1, np.int32)
+    offs[1 * 3 + 2 + 1:] = 1
+    one = orc.sgemm_fma_pieces(0, 0, 1, A, B, M, N, K, bm, bn, offs, np.array([40], np.int32)).reshape(M, N)
+    ref = none.reshape(M, N).copy()
+    a2, b2 = A.reshape(M, K), B.reshape(N, K)  # A row-major, B col-major
+    for i in range(32, 64):
+        for j in range(64, 80):
+            p0 = np.float32(0)
+            for k in range(40):
+                p0 = np.float32(np.float64(a2[i, k]) * np.float64(b2[j, k]) + np.float64(p0))
+            p1 = np.float32(0)
+            for k in range(40, K):
+                p1 = np.float32(np.float64(a2[i, k]) * np.float64(b2[j, k]) + np.float64(p1))
+            ref[i, j] = np.float32(p0 + p1)
+    assert np.array_equal(one.view(np.uint32), ref.view(np.uint32))
