@@ -155,6 +155,13 @@ int b200_sgemm_fma_peak(int mode, int iterations, float* elapsed_ms, double* flo
  * reference has no counterpart because its kernel has no waits that could time out. */
 int b200_sgemm_device_status(int* status);
 
+/* Self-test of the kernels' bounded waits, safe to run on any device: launches a private copy of the
+ * warp-specialised kernel whose wait limit is one millisecond on a single 128 x 128 x 64 tile (A: 128 x 64 col-major,
+ * B: 64 x 128 row-major, C: 128 x 128 row-major device buffers, A and B 16-byte aligned) and withholds the second K
+ * tile from it.  The consumer warps give up after the limit, record status 1 and return; C is left untouched.
+ * Afterwards b200_sgemm_device_status() reads 1 once and 0 from then on.  Nothing traps and nothing stays in flight. */
+int b200_sgemm_selftest_bounded_wait(float* C, const float* A, const float* B, void* cuda_stream);
+
 /* The same operation for matrices in HOST memory: uploads row panels of A and column panels of B
  * alternately, computes the rectangle of C that each upload completes as one GEMM, downloads it when it
  * is done (upload, compute and download overlap on internal streams), and returns when C is

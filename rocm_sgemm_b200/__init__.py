@@ -89,7 +89,8 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
            "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
-           "b200_sgemm_blas_shutdown", "b200_sgemm_multi", "b200_sgemm_stream_plan")
+           "b200_sgemm_blas_shutdown", "b200_sgemm_multi", "b200_sgemm_stream_plan",
+           "b200_sgemm_selftest_bounded_wait")
 
 
 def lib() -> ctypes.CDLL:
@@ -125,6 +126,7 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_blas.argtypes = [i, i, _sz, _sz, _sz, ctypes.c_float, _vp, _sz, _vp, _sz, ctypes.c_float, _vp, _sz, _vp]
     ip = ctypes.POINTER(i)
     l.b200_sgemm_stream_plan.argtypes = [i, i, i, _sz, _sz, _sz, i, i, i, ip, ip, ip, i]
+    l.b200_sgemm_selftest_bounded_wait.argtypes = [_vp, _vp, _vp, _vp]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
     _lib = l
@@ -336,6 +338,12 @@ def fma_peak(mode: int = 1, iterations: int = 4096, stream=None) -> dict:
     ms, fl = ctypes.c_float(), ctypes.c_double()
     _check(lib().b200_sgemm_fma_peak(mode, iterations, ctypes.byref(ms), ctypes.byref(fl), _stream(stream)))
     return {"ms": ms.value, "flops": fl.value, "tflops": fl.value / (ms.value * 1e-3) / 1e12}
+
+
+def selftest_bounded_wait(C, A, B, stream=None) -> None:
+    """Launches the one-tile self-test whose consumers run into their (1 ms) wait limit; device_status() then reads
+    1 once.  C: 128*128 floats, A: 128*64, B: 64*128 device buffers."""
+    _check(lib().b200_sgemm_selftest_bounded_wait(_ptr(C), _ptr(A), _ptr(B), _stream(stream)))
 
 
 def device_status() -> int:

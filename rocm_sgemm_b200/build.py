@@ -110,6 +110,7 @@ def build_library(config: Path | None = None, jobs: int | None = None, verbose=F
     work.append((CSRC / "sgemm_host.cu", [REPO / "include" / "b200_sgemm.h"]))
     work.append((CSRC / "sgemm_tf32x3.cu", kernel_hdr + [CSRC / "transpose.hpp", REPO / "include" / "b200_sgemm.h"]))
     work.append((CSRC / "sgemm_blas.cu", [REPO / "include" / "b200_sgemm.h"]))
+    work.append((CSRC / "sgemm_selftest.cu", kernel_hdr + [REPO / "include" / "b200_sgemm.h"]))
     objs = []
     with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
         futs = [ex.submit(_compile, s, d, NVCC_FLAGS, verbose, ptxas_log) for s, d in work]

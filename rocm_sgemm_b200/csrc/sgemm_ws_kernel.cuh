@@ -61,8 +61,14 @@ __host__ __device__ constexpr int ws_producer_threads(int consumer_threads, int 
     return (consumer_threads >= 256 && accumulators_per_thread <= 64) ? 128 : 64;
 }
 constexpr int      WS_MAX_EXTRA     = 7; // peers of an 8-GPU node
+#ifdef WS_SELFTEST_LIMITS
+// the self-test's private copy of the kernel (sgemm_selftest.cu) gives up after a millisecond
+constexpr uint32_t WS_SPIN_LIMIT    = 1u << 10;
+constexpr uint64_t WS_WAIT_LIMIT_NS = 1000ull * 1000ull;
+#else
 constexpr uint32_t WS_SPIN_LIMIT    = 1u << 22;
 constexpr uint64_t WS_WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull; // one second per wait
+#endif
 
 // status word values written by the kernel (0 = ok)
 constexpr int WS_ERR_FULL_TIMEOUT  = 1; // a consumer gave up waiting for a stage to fill
@@ -84,9 +90,15 @@ struct WsArgs
     // schedules 1 and 2 (see the head of this file)
     int       sched;
     int       k_tiles;  // K tiles per tile: ceil(K / block_k)
+    int       rr_tiles; // schedule 1: this many leading tiles (a multiple of gridDim.x) are dealt round-robin as whole
+                        // tiles first - neighbouring CTAs then work on neighbouring tiles, which the L2 likes -
+                        // and only the rest (between one and two waves) is cut into equal ranges
     float*    handover; // gridDim.x slots of block_m x block_n floats: slot c holds what CTA c parked
     unsigned* flags;    // one word per (CTA, consumer warp): == epoch once that warp's part of slot c is complete
     unsigned  epoch;    // differs from launch to launch, so the words never need clearing
+    // Self-test only (0 everywhere else): the thread that issues the TMA copies leaves out the very last K tile of its
+    // last piece - no copy, no arrival - so the consumers' wait for that stage runs into its limit.
+    int       test_omit_last_fill;
 };
 
 // One contiguous piece of work of a CTA: K range [k_begin, k_end) of one tile.
@@ -117,6 +129,7 @@ struct WsSchedule
     int last_tile, last_a;         // tail piece: K tiles [last_a, kts) of last_tile, last_tile < 0: none
     int last_first;                // schedule 2: the CTA that owns the first piece of last_tile
     int whole0, nwhole, kts;
+    int n_rr, tile0; // schedule 1: whole tiles dealt round-robin before the range, first tile of the ranges
     int bk, K, k_per_split;
 
     __device__ __forceinline__ void init(const WsArgs& w, int tiles_, int BK)
@@ -133,8 +146,10 @@ struct WsSchedule
             n      = first < w.total_units ? (w.total_units - first + stride - 1) / stride : 0;
             return;
         }
-        kts = w.k_tiles;
-        const long long units = (long long)tiles * kts;
+        kts   = w.k_tiles;
+        tile0 = sched == 1 ? w.rr_tiles : 0;
+        n_rr  = tile0 / (int)gridDim.x;
+        const long long units = (long long)(tiles - tile0) * kts;
         const long long u0    = ws_range_begin(units, gridDim.x, blockIdx.x);
         const long long u1    = ws_range_begin(units, gridDim.x, blockIdx.x + 1);
         park_tile = last_tile = -1;
@@ -166,7 +181,7 @@ struct WsSchedule
                 last_first = c;
             }
         }
-        n = (park_tile >= 0 ? 1 : 0) + nwhole + (last_tile >= 0 ? 1 : 0);
+        n = n_rr + (park_tile >= 0 ? 1 : 0) + nwhole + (last_tile >= 0 ? 1 : 0);
     }
     __device__ __forceinline__ WsPiece piece(int i) const
     {
@@ -182,23 +197,31 @@ struct WsSchedule
             p.k_end        = min(K, p.k_begin + k_per_split);
             return p;
         }
+        if(i < n_rr)
+        {
+            p.tile_id = (int)blockIdx.x + i * (int)gridDim.x;
+            p.k_begin = 0;
+            p.k_end   = K;
+            return p;
+        }
+        i -= n_rr;
         const int h = park_tile >= 0 ? 1 : 0;
         if(h && i == 0)
         {
-            p.tile_id = park_tile; // first of all: the piece somebody else waits for
+            p.tile_id = tile0 + park_tile; // first of the range: the piece somebody else waits for
             p.k_begin = park_a * bk;
             p.k_end   = park_b * bk; // < K: a parked piece never reaches the last K tile
             p.send    = blockIdx.x;
         }
         else if(i - h < nwhole)
         {
-            p.tile_id = whole0 + (i - h);
+            p.tile_id = tile0 + whole0 + (i - h);
             p.k_begin = 0;
             p.k_end   = K;
         }
         else
         {
-            p.tile_id = last_tile; // last of all: the tail of the first tile
+            p.tile_id = tile0 + last_tile; // last of all: the tail of the first tile of the range
             p.k_begin = last_a * bk;
             p.k_end   = K;
             if(sched == 1)
@@ -629,6 +652,8 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     return;
                 }
                 const int k0 = k_begin + t * BK;
+                if(w.test_omit_last_fill && pi == sch.n - 1 && t == ntiles - 1)
+                    return; // self-test: this stage is never filled
                 if(ptid == 0)
                 {
                     if(tx_bytes)

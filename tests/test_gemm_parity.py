@@ -436,3 +436,25 @@ def test_reentrant_threads_and_streams(sgemm, orc):
         _, _, dC, A, B = inputs[i]
         expect_bit_exact(sgemm, orc, la, lb, lc, A, B, M, N, K, dC.cpu().numpy())
     assert sgemm.device_status() == 0
+
+
+def test_bounded_wait_gives_up_and_reports(sgemm):
+    """The time-out path of the kernels' waits, made to happen without any fault: the self-test launches a private copy
+    of the warp-specialised kernel (wait limit 1 ms) on one tile and withholds the last K tile, so the consumer
+    warps' wait for that stage runs out.  Every thread returns, the status word reads 1 (consumer-side time-out) once
+    and 0 afterwards, C is untouched, and the device computes correctly right after."""
+    dA = torch.rand(128 * 64, dtype=torch.float32, device="cuda")
+    dB = torch.rand(64 * 128, dtype=torch.float32, device="cuda")
+    dC = torch.full((128 * 128,), 7.0, dtype=torch.float32, device="cuda")
+    assert sgemm.device_status() == 0
+    sgemm.selftest_bounded_wait(dC, dA, dB)
+    torch.cuda.synchronize()  # the kernel ended by itself
+    assert sgemm.device_status() == 1
+    assert sgemm.device_status() == 0
+    assert bool((dC == 7.0).all())
+    # the context is healthy: an ordinary product right after is exact
+    sgemm.gemm(0, 1, 0, dC, dA, dB, 128, 128, 64)
+    torch.cuda.synchronize()
+    ref = dA.view(64, 128).T.double() @ dB.view(64, 128).double()
+    assert float((dC.view(128, 128).double() - ref).abs().max()) < 1e-4
+    assert sgemm.device_status() == 0
