@@ -79,6 +79,15 @@ int b200_sgemm_ex(int layout_c, int layout_a, int layout_b, float* C, const floa
                   size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant, int split_k, void* workspace,
                   size_t workspace_bytes, void* cuda_stream);
 
+/* One tuning trial: exactly what b200_sgemm does for a problem whose table entry names this kernel variant,
+ * split_k (1 = none, n >= 2 = n slices + reduction kernel, 0 = equal K ranges per CTA) and pretranspose bits
+ * (bit 0 / 1: copy a K-contiguous A / B transposed into the arena first) - scratch from the library's arena, the
+ * balanced schedules where they apply.  The tuner times candidates through this entry, so that every property of
+ * a table entry is searched through the path the drop-in entry takes; the reference's tuner launches its
+ * JIT-compiled instantiation directly (rocm_sgemm/config/tuner.cpp:419-429). */
+int b200_sgemm_trial(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,
+                     size_t N, size_t K, int variant, int split_k, int pretranspose, void* cuda_stream);
+
 /* The product written to several destinations at once: C_list[0 .. n_dst-1] (1 <= n_dst <= 8) all receive the
  * M x N result with the same layout and leading dimension; the kernel's epilogue stores every tile to each of them.
  * Meant for the column-sharded multi-GPU product: each GPU passes the position of its own column block inside its

@@ -90,7 +90,7 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
            "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
            "b200_sgemm_blas_shutdown", "b200_sgemm_multi", "b200_sgemm_stream_plan",
-           "b200_sgemm_selftest_bounded_wait")
+           "b200_sgemm_selftest_bounded_wait", "b200_sgemm_trial")
 
 
 def lib() -> ctypes.CDLL:
@@ -127,6 +127,7 @@ def lib() -> ctypes.CDLL:
     ip = ctypes.POINTER(i)
     l.b200_sgemm_stream_plan.argtypes = [i, i, i, _sz, _sz, _sz, i, i, i, ip, ip, ip, i]
     l.b200_sgemm_selftest_bounded_wait.argtypes = [_vp, _vp, _vp, _vp]
+    l.b200_sgemm_trial.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, i, i, _vp]
     l.b200_sgemm_status_string.argtypes = [i]
     l.b200_sgemm_status_string.restype = ctypes.c_char_p
     _lib = l
@@ -182,6 +183,13 @@ def gemm_ex(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, lda: 
     """The explicit form: leading dimensions (0 = packed), forced variant / split-K, caller workspace."""
     _check(lib().b200_sgemm_ex(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K, lda,
                                ldb, ldc, variant, split_k, _ptr(workspace), workspace_bytes, _stream(stream)))
+
+
+def gemm_trial(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, variant: int, split_k: int = 1,
+               pretranspose: int = 0, stream=None) -> None:
+    """What gemm() would do if the table entry of this problem named (variant, split_k, pretranspose)."""
+    _check(lib().b200_sgemm_trial(int(layout_c), int(layout_a), int(layout_b), _ptr(C), _ptr(A), _ptr(B), M, N, K, variant,
+                                  split_k, pretranspose, _stream(stream)))
 
 
 def gemm_splitk_static(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: int, split_k: int, stream=None) -> None:

@@ -7,11 +7,18 @@ parameters, constraint pruning that does not consume budget (:100-144, :210-212)
 configurations or the entry of an existing table (:261-279), one process per timed trial with a timeout
 (:163-190), and a merged output JSON in the table's schema (:650-671).  Differences:
 
-  * Optuna is not a dependency: the sampler below is a small categorical TPE (independent per
-    parameter; good / bad split at the best 25 %, Laplace-smoothed category frequencies, the candidate
-    maximising l(x)/g(x) among `n_ei_candidates` draws from l).
+  * Optuna is not a dependency: the sampler below is a small categorical TPE.  Good / bad split at the best
+    25 %; by default MULTIVARIATE like the reference's study (tune.py:248-256, multivariate=True): l(x) and g(x) are
+    Parzen mixtures with one component per observation (a product of per-parameter categorical kernels that keep
+    the observed value with probability 1 - eps), so combinations that work together are proposed together;
+    `--independent` falls back to per-parameter Laplace-smoothed frequencies.  The candidate maximising l(x)/g(x)
+    among `n_ei_candidates` draws from l is tried next.
   * The search space is the CUDA one: the reference's nine tile parameters plus stages, fma_mode,
-    raster, pipeline (kernel variant) and split_k (table entry).
+    raster, pipeline (kernel variant) and split_k, pretranspose (table entry: split_k 0 = equal K ranges per
+    CTA summed inside the kernel; pretranspose bit 0 / 1 = copy a K-contiguous A / B transposed first).  Trials
+    run through b200_sgemm_trial, i.e. the drop-in entry's own path.
+  * --max-memory bounds the dynamic shared memory of a candidate CTA (the reference's LDS limit flag,
+    tune.py:581-582).
   * Candidates are compiled by nvcc a batch at a time into a candidate build of the library
     (rocm_sgemm_b200/build.py), then each is timed by the `tuner` executable in its own process; the
     reference JIT-compiles inside its tuner with hipRTC instead.
@@ -54,42 +61,71 @@ SPACE = {
     "raster": [0, 1],
     "min_blocks": [1, 2],
     "pipeline": [0, 1],
-    "split_k": [1, 2, 3, 4, 6, 8, 12, 16],
+    "split_k": [0, 1, 2, 3, 4, 6, 8, 12, 16],
+    "pretranspose": [0, 1, 2, 3],
 }
+ENTRY_KEYS = ("split_k", "pretranspose")  # table-entry properties; the rest are kernel-variant parameters
+MAX_SMEM = 227 * 1024
 BASELINES = [
-    # (14 variant parameters), split_k
-    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 1),
-    ((256, 128, 128, 16, 2, 2, 4, 4, 8, 6, 1, 1, 1, 1), 1),
-    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 3, 1, 0, 1, 1), 1),
-    ((256, 128, 128, 16, 2, 2, 4, 4, 8, 2, 1, 1, 2, 0), 1),
-    ((128, 128, 64, 16, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 1),
-    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 2),
-    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 4),
+    # (14 variant parameters), split_k, pretranspose (masked to the layout's K-contiguous operands)
+    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 1, 3),
+    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 1, 0),
+    ((256, 128, 128, 32, 2, 2, 4, 4, 16, 4, 1, 1, 1, 1), 1, 3),
+    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 3, 1, 0, 1, 1), 1, 3),
+    ((256, 128, 128, 16, 2, 2, 4, 4, 8, 2, 1, 1, 2, 0), 1, 0),
+    ((128, 128, 64, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 1, 0),
+    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 0, 0),
+    ((256, 128, 128, 32, 2, 2, 4, 4, 8, 4, 1, 1, 1, 1), 2, 0),
 ]
 LAYOUT_NAMES = {0: "row_major", 1: "col_major"}
 
 
-def valid(cfg: dict) -> bool:
-    """Constraint check: the generator's (shared with the build) plus the split-K sanity bound."""
+def smem_bytes(cfg: dict, layout=None) -> int:
+    """Dynamic shared memory of a candidate CTA: the stage ring, and for the warp-specialised kernel its barriers
+    and the staging ring of K-contiguous operands that are not pre-transposed."""
+    b = cfg["stages"] * (cfg["block_m"] + cfg["block_n"]) * cfg["block_k"] * 4
+    if cfg["pipeline"] >= 1:
+        b += (2 * cfg["stages"] + 4) * 8 + 16
+        if layout is not None and cfg["block_k"] == 32:
+            pre = cfg.get("pretranspose", 0)
+            sa = layout[0] == 0 and not (pre & 1)
+            sb = layout[1] == 1 and not (pre & 2)
+            if sa or sb:
+                b += 1024 + 2 * ((cfg["block_m"] * 128 if sa else 0) + (cfg["block_n"] * 128 if sb else 0))
+    return b
+
+
+def valid(cfg: dict, layout=None, max_memory: int = MAX_SMEM) -> bool:
+    """Constraint check: the generator's (shared with the build), the table-entry properties, the memory bound."""
     v = tuple(cfg[n] for n in NAMES)
     if gc.check_variant(v) is not None:
         return False
     if cfg["pipeline"] == 0 and cfg["fma_mode"] not in (0, 1, 2):
         return False
-    return cfg["split_k"] >= 1
+    if cfg["split_k"] < 0 or not 0 <= cfg.get("pretranspose", 0) <= 3:
+        return False
+    if cfg["pipeline"] == 0 and (cfg.get("pretranspose", 0) or cfg["split_k"] == 0):
+        return False  # both belong to the warp-specialised kernel
+    if layout is not None:
+        # only K-contiguous operands can be pre-transposed: other bits would duplicate configurations
+        allowed = (1 if layout[0] == 0 else 0) | (2 if layout[1] == 1 else 0)
+        if cfg.get("pretranspose", 0) & ~allowed:
+            return False
+    return smem_bytes(cfg) <= max_memory
 
 
 def count_valid() -> int:
     """Size of the valid search space (the reference reports 18 060 of 262 144 for its own)."""
     import itertools
     keys = list(SPACE)
-    return sum(valid(dict(zip(keys, combo))) for combo in itertools.product(*(SPACE[k] for k in keys)))
+    return sum(valid(dict(zip(keys, combo)), (0, 1, 0)) for combo in itertools.product(*(SPACE[k] for k in keys)))
 
 
 class CategoricalTPE:
-    def __init__(self, space, seed=0, gamma=0.25, n_startup=10, n_ei_candidates=24):
+    def __init__(self, space, seed=0, gamma=0.25, n_startup=10, n_ei_candidates=24, multivariate=True, eps=0.25):
         self.space, self.rng = space, random.Random(seed)
         self.gamma, self.n_startup, self.n_ei = gamma, n_startup, n_ei_candidates
+        self.multivariate, self.eps = multivariate, eps
         self.obs = []  # (cfg, value), lower is better; failed trials carry math.inf
 
     def tell(self, cfg, value):
@@ -117,14 +153,33 @@ class CategoricalTPE:
                     s = sum(w)
                     return [x / s for x in w]
 
+                def mixture(group, c):
+                    """Parzen mixture over the observations of `group` plus a uniform prior component."""
+                    total = 1.0
+                    for key, values in self.space.items():
+                        total /= len(values)
+                    for o in group:
+                        p = 1.0
+                        for key, values in self.space.items():
+                            p *= (1.0 - self.eps) if c[key] == o[key] else self.eps / max(1, len(values) - 1)
+                        total += p
+                    return total / (len(group) + 1)
+
                 best, best_score = None, -math.inf
                 for _ in range(self.n_ei):
                     c, score = {}, 0.0
-                    for key, values in self.space.items():
-                        pl, pg = dist(good, key), dist(bad, key)
-                        i = self.rng.choices(range(len(values)), weights=pl)[0]
-                        c[key] = values[i]
-                        score += math.log(pl[i]) - math.log(pg[i])
+                    if self.multivariate:
+                        # draw from l: one good observation, each parameter kept with probability 1 - eps
+                        o = self.rng.choice(good) if self.rng.random() < len(good) / (len(good) + 1.0) else self._random()
+                        for key, values in self.space.items():
+                            c[key] = o[key] if self.rng.random() >= self.eps else self.rng.choice(values)
+                        score = math.log(mixture(good, c)) - math.log(mixture(bad, c))
+                    else:
+                        for key, values in self.space.items():
+                            pl, pg = dist(good, key), dist(bad, key)
+                            i = self.rng.choices(range(len(values)), weights=pl)[0]
+                            c[key] = values[i]
+                            score += math.log(pl[i]) - math.log(pg[i])
                     if score > best_score and is_valid(c) and tuple(sorted(c.items())) not in seen:
                         best, best_score = c, score
                 cand = best or self._random()
@@ -155,8 +210,15 @@ def time_candidates(cands, shape, layout, workdir: Path, iters=20, timeout=60):
     empty.write_text('{"configurations": []}')
     variants = [tuple(c[n] for n in NAMES) for c in cands]
     lib = workdir / "libcandidate.so"
+    pairs = []
+    for c, v in zip(cands, variants):
+        pre = c.get("pretranspose", 0)
+        # a pre-transposed operand reaches the kernel as an M / N-contiguous one: those instantiations are needed too
+        for a in {layout[0], 1 if pre & 1 else layout[0]}:
+            for bb in {layout[1], 0 if pre & 2 else layout[1]}:
+                pairs.append((v, (a, bb, layout[2])))
     try:
-        b.build_library(config=empty, extra_pairs=[(v, layout) for v in variants], out=lib)
+        b.build_library(config=empty, extra_pairs=pairs, out=lib)
     except RuntimeError as e:  # one bad candidate fails the batch: fall back to one library per candidate
         if len(cands) == 1:
             return [math.inf]
@@ -169,7 +231,8 @@ def time_candidates(cands, shape, layout, workdir: Path, iters=20, timeout=60):
         build_tuner_exe(exe)
     results = []
     for c, v in zip(cands, variants):
-        args = [str(exe), str(lib), *map(str, shape), *map(str, v), str(c["split_k"]), *map(str, layout), str(iters), "3"]
+        args = [str(exe), str(lib), *map(str, shape), *map(str, v), str(c["split_k"]), str(c.get("pretranspose", 0)),
+                *map(str, layout), str(iters), "3"]
         try:
             r = subprocess.run(args, capture_output=True, text=True, timeout=timeout)
             t = parse_time(r.stdout) if r.returncode == 0 else None
@@ -179,22 +242,28 @@ def time_candidates(cands, shape, layout, workdir: Path, iters=20, timeout=60):
     return results
 
 
-def tune_problem(shape, layout, budget, seed, journal: Path, workdir: Path, batch=8, seeds=()):
+def tune_problem(shape, layout, budget, seed, journal: Path, workdir: Path, batch=8, seeds=(), multivariate=True,
+                 max_memory=MAX_SMEM):
     key = {"shape": list(shape), "layout": list(layout)}
-    tpe = CategoricalTPE(SPACE, seed=seed, n_startup=min(10, max(1, budget // 4)))
+    tpe = CategoricalTPE(SPACE, seed=seed, n_startup=min(10, max(1, budget // 4)), multivariate=multivariate)
+    allowed = (1 if layout[0] == 0 else 0) | (2 if layout[1] == 1 else 0)
+
+    def ok(c):
+        return valid(c, layout, max_memory)
     # resume: replay the journal
     if journal.exists():
         for line in journal.read_text().splitlines():
             rec = json.loads(line)
-            if rec["shape"] == key["shape"] and rec["layout"] == key["layout"]:
+            if rec["shape"] == key["shape"] and rec["layout"] == key["layout"] and "pretranspose" in rec["config"]:
                 tpe.tell(rec["config"], rec["ms"] if rec["ms"] is not None else math.inf)
-    queue = [dict(zip(NAMES, v), split_k=s) for v, s in seeds if valid(dict(zip(NAMES, v), split_k=s))]
+    queue = [dict(zip(NAMES, v), split_k=s, pretranspose=p & allowed) for v, s, p in seeds]
+    queue = [c for c in queue if ok(c)]
     tried = {tuple(sorted(c.items())) for c, _ in tpe.obs}
     queue = [c for c in queue if tuple(sorted(c.items())) not in tried]
     while len(tpe.obs) < budget:
         cands = []
         while len(cands) < min(batch, budget - len(tpe.obs)):
-            c = queue.pop(0) if queue else tpe.ask(valid)
+            c = queue.pop(0) if queue else tpe.ask(ok)
             if c is None:
                 break
             if c not in cands:
@@ -217,8 +286,7 @@ def tune_problem(shape, layout, budget, seed, journal: Path, workdir: Path, batc
 def entry(shape, layout, cfg):
     conf = {n: cfg[n] for n in NAMES}
     conf["split_k"] = cfg["split_k"]
-    # K-contiguous operands may be pre-transposed by the drop-in entry when the problem is large
-    conf["pretranspose"] = (1 if layout[0] == 0 else 0) | (2 if layout[1] == 1 else 0) if cfg["pipeline"] >= 1 else 0
+    conf["pretranspose"] = cfg.get("pretranspose", 0)
     return {"range": dict(zip("MNK", shape)), "layout": {k: LAYOUT_NAMES[x] for k, x in zip("ABC", layout)}, "config": conf}
 
 
@@ -231,7 +299,7 @@ def table_seed(table, shape, layout):
     for e in table:
         r, l = e["range"], e["layout"]
         if (r["M"], r["N"], r["K"]) == tuple(shape) and tuple(gc.LAYOUT_VAL[l[k]] for k in "ABC") == tuple(layout):
-            return [(gc.variant_of(e["config"]), int(e["config"].get("split_k", 1)))]
+            return [(gc.variant_of(e["config"]), int(e["config"].get("split_k", 1)), int(e["config"].get("pretranspose", 0)))]
     return []
 
 
@@ -246,6 +314,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="candidates compiled per build")
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--gpu-arch", default="sm_100a", help="kept for the reference's CLI; only sm_100a is built")
+    ap.add_argument("--max-memory", type=int, default=MAX_SMEM,
+                    help="dynamic shared memory a candidate CTA may use, bytes (default: the 227 KB an SM offers)")
+    ap.add_argument("--independent", action="store_true", help="per-parameter TPE instead of the multivariate one")
     ap.add_argument("--journal", default="tune_journal.jsonl")
     ap.add_argument("--output", default="gemm_config_tuned.json")
     ap.add_argument("--count-space", action="store_true", help="print the size of the valid search space and exit")
@@ -268,7 +339,8 @@ def main():
             for layout in layouts:
                 print(f"tuning {shape} layout {gc.layout_str(*layout)}", flush=True)
                 seeds = table_seed(table, shape, layout) + BASELINES[:a.baselines]
-                best = tune_problem(shape, layout, a.budget, a.seed, journal, Path(tmp), a.batch, seeds)
+                best = tune_problem(shape, layout, a.budget, a.seed, journal, Path(tmp), a.batch, seeds,
+                                    multivariate=not a.independent, max_memory=a.max_memory)
                 if best:
                     e = entry(shape, layout, best[0])
                     merged[(e["range"]["M"], e["range"]["N"], e["range"]["K"], e["layout"]["A"], e["layout"]["B"],

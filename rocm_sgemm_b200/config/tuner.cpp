@@ -6,10 +6,12 @@
 // configuration cannot take the search down.  Here the candidate kernels are compiled by nvcc into a
 // candidate build of the library (tune.py does that, a batch at a time, through
 // rocm_sgemm_b200/build.py) and this program loads that build, finds the variant whose parameters match
-// the command line and times it through b200_sgemm_ex, bypassing the tuned table exactly as the
-// reference's tuner bypasses its gemm() entry (tuner.cpp:419-429).
+// the command line and times it through b200_sgemm_trial: the drop-in entry's own path (arena scratch,
+// pre-transposition, split-K or the balanced schedules) with the candidate standing in for the table entry, so
+// that every property of an entry is searched through the code that will use it.  (The reference's tuner launches
+// its JIT-compiled kernel directly, tuner.cpp:419-429; its table entries have no property beyond the kernel.)
 //
-//   tuner <library.so> M N K  <14 variant parameters>  split_k  layout_A layout_B layout_C  [iters] [warmup]
+//   tuner <library.so> M N K  <14 variant parameters>  split_k pretranspose  layout_A layout_B layout_C  [iters] [warmup]
 //
 // Inputs are the reference benchmark's cyclic five-value pattern (tuner.cpp:105-120).  Output, one line:
 //   manual_time <mean ms> ms min <min ms> ms tflops <avg TFLOP/s>
@@ -59,10 +61,10 @@ F sym(void* lib, const char* name)
 
 int main(int argc, char** argv)
 {
-    if(argc < 23)
+    if(argc < 24)
     {
-        std::fprintf(stderr, "usage: %s <library.so> M N K <14 variant parameters> split_k layout_A layout_B layout_C "
-                             "[iters] [warmup]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s <library.so> M N K <14 variant parameters> split_k pretranspose layout_A layout_B "
+                             "layout_C [iters] [warmup]\n", argv[0]);
         return 1;
     }
     void* lib = dlopen(argv[1], RTLD_NOW | RTLD_LOCAL);
@@ -76,16 +78,15 @@ int main(int argc, char** argv)
     int want[14];
     for(int i = 0; i < 14; ++i)
         want[i] = std::atoi(argv[5 + i]);
-    const int split_k = std::atoi(argv[19]);
-    const int la = std::atoi(argv[20]), lb = std::atoi(argv[21]), lc = std::atoi(argv[22]);
-    const int iters = argc > 23 ? std::atoi(argv[23]) : 20, warmup = argc > 24 ? std::atoi(argv[24]) : 3;
+    const int split_k = std::atoi(argv[19]), pretranspose = std::atoi(argv[20]);
+    const int la = std::atoi(argv[21]), lb = std::atoi(argv[22]), lc = std::atoi(argv[23]);
+    const int iters = argc > 24 ? std::atoi(argv[24]) : 20, warmup = argc > 25 ? std::atoi(argv[25]) : 3;
 
     auto num_variants = sym<int (*)(void)>(lib, "b200_sgemm_num_variants");
     auto get_variant  = sym<int (*)(int, b200_sgemm_params*)>(lib, "b200_sgemm_get_variant");
     auto has_kernel   = sym<int (*)(int, int, int)>(lib, "b200_sgemm_has_kernel");
-    auto ws_bytes     = sym<size_t (*)(int, int, int, size_t, size_t, size_t, int, int)>(lib, "b200_sgemm_workspace_bytes");
-    auto gemm_ex      = sym<int (*)(int, int, int, float*, const float*, const float*, size_t, size_t, size_t, size_t,
-                               size_t, size_t, int, int, void*, size_t, void*)>(lib, "b200_sgemm_ex");
+    auto gemm_trial   = sym<int (*)(int, int, int, float*, const float*, const float*, size_t, size_t, size_t, int, int, int,
+                                    void*)>(lib, "b200_sgemm_trial");
     auto status_str   = sym<const char* (*)(int)>(lib, "b200_sgemm_status_string");
 
     int variant = -1;
@@ -109,13 +110,9 @@ int main(int argc, char** argv)
     fill_pattern(hA);
     fill_pattern(hB);
     float *dA, *dB, *dC;
-    void*  ws    = nullptr;
-    size_t wsize = ws_bytes(lc, la, lb, M, N, K, variant, split_k);
     CHECK(cudaMalloc(&dA, hA.size() * sizeof(float)));
     CHECK(cudaMalloc(&dB, hB.size() * sizeof(float)));
     CHECK(cudaMalloc(&dC, M * N * sizeof(float)));
-    if(wsize)
-        CHECK(cudaMalloc(&ws, wsize));
     CHECK(cudaMemcpy(dA, hA.data(), hA.size() * sizeof(float), cudaMemcpyHostToDevice));
     CHECK(cudaMemcpy(dB, hB.data(), hB.size() * sizeof(float), cudaMemcpyHostToDevice));
     cudaStream_t stream;
@@ -128,10 +125,12 @@ int main(int argc, char** argv)
     for(int i = 0; i < warmup + iters; ++i)
     {
         CHECK(cudaEventRecord(e0, stream));
-        const int st = gemm_ex(lc, la, lb, dC, dA, dB, M, N, K, 0, 0, 0, variant, split_k, ws, wsize, stream);
+        // the path of the drop-in entry with this candidate as the table entry: arena scratch, pre-transposition,
+        // split-K or the balanced schedules
+        const int st = gemm_trial(lc, la, lb, dC, dA, dB, M, N, K, variant, split_k, pretranspose, stream);
         if(st != 0)
         {
-            std::fprintf(stderr, "b200_sgemm_ex: %s\n", status_str(st));
+            std::fprintf(stderr, "b200_sgemm_trial: %s\n", status_str(st));
             return st > 0 ? 3 : 2;
         }
         CHECK(cudaEventRecord(e1, stream));

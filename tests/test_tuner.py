@@ -58,14 +58,47 @@ def test_parse_time():
     assert tune.parse_time("CUDA error") is None
 
 
-def test_entry_schema_and_pretranspose_bits():
-    cfg = dict(zip(tune.NAMES, tune.BASELINES[0][0]), split_k=2)
+def test_entry_schema_and_searched_entry_properties():
+    cfg = dict(zip(tune.NAMES, tune.BASELINES[0][0]), split_k=2, pretranspose=3)
     e = tune.entry((4096, 4096, 4096), (0, 1, 0), cfg)
     assert e["range"] == {"M": 4096, "N": 4096, "K": 4096}
     assert e["layout"] == {"A": "row_major", "B": "col_major", "C": "row_major"}
     assert e["config"]["split_k"] == 2 and e["config"]["pretranspose"] == 3
     assert tune.gc.check_variant(tune.gc.variant_of(e["config"])) is None
-    assert tune.entry((64, 64, 64), (1, 0, 0), cfg)["config"]["pretranspose"] == 0
+    # pre-transposition is a searched property: only bits of K-contiguous operands are valid for a layout
+    assert tune.valid(cfg, (0, 1, 0)) and not tune.valid(cfg, (1, 1, 0)) and not tune.valid(cfg, (1, 0, 0))
+    assert tune.valid(dict(cfg, pretranspose=2), (1, 1, 0)) and tune.valid(dict(cfg, pretranspose=0), (1, 0, 0))
+    # split_k 0 (equal K ranges per CTA) belongs to the warp-specialised kernel only
+    assert tune.valid(dict(cfg, split_k=0, pretranspose=0), (0, 0, 0))
+    assert not tune.valid(dict(cfg, split_k=0, pretranspose=0, pipeline=0, fma_mode=2), (0, 0, 0))
+
+
+def test_max_memory_bound():
+    cfg = dict(zip(tune.NAMES, tune.BASELINES[0][0]), split_k=1, pretranspose=0)
+    need = tune.smem_bytes(cfg)
+    assert need == 4 * (128 + 128) * 32 * 4 + (2 * 4 + 4) * 8 + 16
+    assert tune.valid(cfg, (1, 0, 0), max_memory=need) and not tune.valid(cfg, (1, 0, 0), max_memory=need - 1)
+    # a K-contiguous operand that is not pre-transposed adds the staging ring
+    assert tune.smem_bytes(cfg, (0, 0, 0)) == need + 1024 + 2 * 128 * 128
+
+
+def test_multivariate_sampler_follows_joint_structure():
+    """A cost whose optimum needs two parameters to agree (block_m == block_n): the multivariate sampler reaches it
+    at least as well as the independent one on average."""
+    def cost(c):
+        return 1.0 + (0.0 if c["block_m"] == c["block_n"] else 1.0) + 0.2 * abs(math.log2(c["block_k"]) - 5) \
+            + (0.0 if c["pipeline"] == 1 else 0.5)
+
+    def run(multivariate, seed, trials=60):
+        tpe = tune.CategoricalTPE(tune.SPACE, seed=seed, n_startup=10, multivariate=multivariate)
+        for _ in range(trials):
+            c = tpe.ask(tune.valid)
+            tpe.tell(c, cost(c))
+        good = sorted(v for _, v in tpe.obs)[:10]
+        return sum(good) / len(good)
+    joint = sum(run(True, s) for s in range(6)) / 6
+    indep = sum(run(False, s) for s in range(6)) / 6
+    assert joint <= indep + 0.05
 
 
 def test_resume_from_journal(tmp_path, monkeypatch):
