@@ -55,7 +55,11 @@ namespace sgemm_b200
 // 256 + 64 threads per CTA the launch bound itself allows 204, so the compiler allocates them directly.  (Handing
 // registers over from a producer warpgroup with setmaxnreg also works, but the code the compiler made for the
 // enlarged budget moved values between registers about ten times per k-step - counted with the profiler's
-// per-opcode instruction counters - and ran at 80 % of the FMA rate where the same loop alone reaches 93 %.)
+// per-opcode instruction counters - and ran at 80 % of the FMA rate where the same loop alone reaches 93 %.  The
+// launch bound cannot be raised by dropping warps either: with nine to twelve warps per CTA an SM sub-partition
+// holds three of them and the compiler's bound is 168 whatever the thread count; only eight warps allow 255, and
+// a build without producer warps - one consumer thread issuing the TMA copies between its FMAs - measured 3 %
+// slower with the 8 x 8 tile and 60.9 TFLOP/s with the 16 x 8 tile at 8192^3.)
 __host__ __device__ constexpr int ws_producer_threads(int consumer_threads, int accumulators_per_thread)
 {
     return (consumer_threads >= 256 && accumulators_per_thread <= 64) ? 128 : 64;
@@ -968,7 +972,6 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
         {
             // schedule 2: this CTA owns the last K range of the tile.  Total = ((p_first + p_next) + ...) + own, in
             // ascending K order; each earlier piece was parked by its CTA before that CTA did anything else.
-            float sum[TMT][TNT];
             for(int src_cta = pc.reduce; src_cta < (int)blockIdx.x; ++src_cta)
             {
                 const unsigned* flag = w.flags + src_cta * CONSUMER_WARPS + warp_id;
@@ -993,27 +996,21 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     }
                     return;
                 }
-                const float4* src = reinterpret_cast<const float4*>(w.handover + (size_t)src_cta * (BM * BN)) + tid;
-#pragma unroll
-                for(int v = 0; v < ACC_VEC; ++v)
-                {
-                    const float4 q = __ldcg(src + v * Cfg::BLOCK_SIZE);
-                    float*       d = &sum[0][0] + 4 * v;
-                    if(src_cta == pc.reduce)
-                    {
-                        d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
-                    }
-                    else
-                    {
-                        d[0] += q.x; d[1] += q.y; d[2] += q.z; d[3] += q.w;
-                    }
-                }
             }
+            // all pieces are there: four accumulators at a time, so that only four partial sums are alive at once
+            const float4* base = reinterpret_cast<const float4*>(w.handover) + tid;
 #pragma unroll
-            for(int i = 0; i < TMT; ++i)
-#pragma unroll
-                for(int j = 0; j < TNT; ++j)
-                    c[i][j] = sum[i][j] + c[i][j];
+            for(int v = 0; v < ACC_VEC; ++v)
+            {
+                float4 sum = __ldcg(base + (size_t)pc.reduce * (BM * BN / 4) + v * Cfg::BLOCK_SIZE);
+                for(int src_cta = pc.reduce + 1; src_cta < (int)blockIdx.x; ++src_cta)
+                {
+                    const float4 q = __ldcg(base + (size_t)src_cta * (BM * BN / 4) + v * Cfg::BLOCK_SIZE);
+                    sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+                }
+                float* d = &c[0][0] + 4 * v;
+                d[0] = sum.x + d[0]; d[1] = sum.y + d[1]; d[2] = sum.z + d[2]; d[3] = sum.w + d[3];
+            }
         }
         store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)pc.split * p.split_stride, m0 + tm0, n0 + tn0);
         for(int d = 0; d < w.n_extra; ++d) // plain stores; to a peer GPU's memory when the pointer is a peer mapping
