@@ -56,12 +56,13 @@ typedef struct b200_sgemm_params
  * Replaces rocm_sgemm::gemm<layout_C, layout_A, layout_B>(C, A, B, M, N, K, stream)
  * (rocm_sgemm/include/rocm_sgemm/gemm.hpp:51-52, rocm_sgemm/src/gemm.cpp:8-41): same argument order
  * (C, A, B), same semantics (alpha = 1, beta = 0, inputs untouched), additionally correct for ragged
- * M, N, K.  A is MxK, B is KxN, C is MxN.  When the tuned table asks for split-K the library takes
- * the partial-sum buffer from an internal per-(device, stream) arena that grows on demand.  Where the
- * table allows it and the problem is large enough for it to pay (the other dimension >= 1024), a
- * K-contiguous operand (row-major A, col-major B) is first copied transposed into the same arena, so
- * that the hot kernel can fetch it with TMA: about 1 % extra time at 4096^3 instead of 5 % lost to
- * transposition inside the kernel.  b200_sgemm_ex never does this: it runs exactly the kernel it is told. */
+ * M, N, K.  A is MxK, B is KxN, C is MxN.  Scratch comes from an internal per-(device, stream) arena that
+ * grows on demand: the accumulator parking slots of the balanced schedules (one CTA tile per SM, whenever the
+ * tiles do not fill the last wave), split-K partial sums where the tuned table still slices K, and, where the
+ * table entry asks for it and the problem is large enough for it to pay (the other dimension >= 1024), the
+ * transposed copy of a K-contiguous operand (row-major A, col-major B), so that the hot kernel can fetch it
+ * straight with TMA: about 1 % extra time at 4096^3 instead of 3.5 % for the transposition inside the
+ * kernel.  b200_sgemm_ex never copies an operand: it runs exactly the kernel it is told. */
 int b200_sgemm(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M, size_t N,
                size_t K, void* cuda_stream);
 
@@ -220,8 +221,8 @@ int b200_sgemm_blas_shutdown(void);
  * split into two TF32 halves and three products per pair ("3xTF32").  The result differs from the FP32 FMA
  * chain of b200_sgemm in the last few bits (relative error of about 2e-6 against float64; identity B does not
  * reproduce A bit for bit).  Same arguments as b200_sgemm.  Operands that are not K-contiguous (col-major A,
- * row-major B) or whose rows are not 16-byte aligned are first repacked into a per-device scratch arena
- * (first such call allocates; b200_sgemm_3xtf32_shutdown frees it).  b200_sgemm_3xtf32_device_status
+ * row-major B) or whose rows are not 16-byte aligned are first repacked into scratch kept per (device, stream)
+ * (first such call on a stream allocates; b200_sgemm_3xtf32_shutdown frees it).  b200_sgemm_3xtf32_device_status
  * synchronises the device and returns (and clears) the kernel's status word: 0 unless a bounded wait
  * inside the kernel gave up. */
 int b200_sgemm_3xtf32(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,

@@ -74,6 +74,10 @@ cudaError_t scratch_get(cudaStream_t stream, size_t bytes, void** out)
 }
 } // namespace
 
+extern "C" int b200_sgemm_batched_launch(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
+                                         size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a, size_t stride_b,
+                                         size_t batch, void* cuda_stream); // sgemm_api.cu (not part of the public header)
+
 extern "C" int b200_sgemm_strided_batched(int layout_c, int layout_a, int layout_b, float* C, const float* A,
                                           const float* B, size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a,
                                           size_t stride_b, size_t batch, void* cuda_stream)
@@ -83,6 +87,15 @@ extern "C" int b200_sgemm_strided_batched(int layout_c, int layout_a, int layout
     // C matrices must not overlap; A or B may be shared by the whole batch (stride 0)
     if(batch > 1 && stride_c < M * N)
         return B200_SGEMM_INVALID_ARGUMENT;
+    // One launch for the whole batch where the table's kernel for this problem can do it (warp-specialised, no K
+    // slices): the persistent CTAs walk the tiles of all matrices, so a batch of small problems fills the SMs.
+    if(batch > 1 && C && A && B)
+    {
+        const int st = b200_sgemm_batched_launch(layout_c, layout_a, layout_b, C, A, B, M, N, K, stride_c, stride_a, stride_b,
+                                                 batch, cuda_stream);
+        if(st != B200_SGEMM_NO_KERNEL)
+            return st;
+    }
     for(size_t b = 0; b < batch; ++b)
     {
         const int st = b200_sgemm(layout_c, layout_a, layout_b, C ? C + b * stride_c : nullptr,

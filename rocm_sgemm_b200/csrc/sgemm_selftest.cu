@@ -37,11 +37,12 @@ bool encode(CUtensorMap* map, const float* base, size_t inner, size_t outer, int
     if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess
        || q != cudaDriverEntryPointSuccess)
         return false;
-    const cuuint64_t dims[2]    = {(cuuint64_t)inner, (cuuint64_t)outer};
-    const cuuint64_t strides[1] = {(cuuint64_t)inner * sizeof(float)};
-    const cuuint32_t box[2]     = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
-    const cuuint32_t estr[2]    = {1, 1};
-    return reinterpret_cast<EncodeTiledFn>(p)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims,
+    // (the kernel's tensor maps carry a batch dimension: extent 1 here)
+    const cuuint64_t dims[3]    = {(cuuint64_t)inner, (cuuint64_t)outer, 1};
+    const cuuint64_t strides[2] = {(cuuint64_t)inner * sizeof(float), (cuuint64_t)inner * outer * sizeof(float)};
+    const cuuint32_t box[3]     = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
+    const cuuint32_t estr[3]    = {1, 1, 1};
+    return reinterpret_cast<EncodeTiledFn>(p)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims,
                                               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
@@ -73,6 +74,7 @@ extern "C" int b200_sgemm_selftest_bounded_wait(float* C, const float* A, const 
     w.status = status;
     w.k_tiles = K / Cfg::BK;
     w.test_omit_last_fill = 1;
+    w.batch = 1;
     CUtensorMap map_a, map_b;
     w.tma_a = encode(&map_a, A, M, K, Cfg::BM, Cfg::BK);
     w.tma_b = encode(&map_b, B, N, K, Cfg::BN, Cfg::BK);

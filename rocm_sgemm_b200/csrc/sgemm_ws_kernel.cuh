@@ -100,6 +100,12 @@ struct WsArgs
     float*    handover; // gridDim.x slots of block_m x block_n floats: slot c holds what CTA c parked
     unsigned* flags;    // one word per (CTA, consumer warp): == epoch once that warp's part of slot c is complete
     unsigned  epoch;    // differs from launch to launch, so the words never need clearing
+    // Batch of equal problems at fixed element strides (batch 1: one problem).  The tile sequence of all schedules is
+    // then batch x (grid_m x grid_n) long: tile id = matrix * tiles_per_matrix + tile.  The tensor maps carry the
+    // batch as one more dimension; bstep_a / bstep_b are 0 for an operand that all problems share.
+    int       batch;
+    int       bstep_a, bstep_b;
+    long long stride_a, stride_b, stride_c;
     // Self-test only (0 everywhere else): the thread that issues the TMA copies leaves out the very last K tile of its
     // last piece - no copy, no arrival - so the consumers' wait for that stage runs into its limit.
     int       test_omit_last_fill;
@@ -365,6 +371,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
                  : "memory");
 }
 
+// (c0, c1, c2, c3) element coordinates of a four-dimensional map
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+                 : "memory");
+}
+
 template<class Cfg>
 struct WsLayout
 {
@@ -508,7 +522,8 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     }
     __syncthreads(); // the only block-wide barrier: everything below is role-local
 
-    const int tiles = p.grid_m * p.grid_n;
+    const int tiles_per_matrix = p.grid_m * p.grid_n;
+    const int tiles            = tiles_per_matrix * w.batch; // the schedules walk the tiles of all matrices of a batch
 
     if(tid >= Cfg::BLOCK_SIZE)
     {
@@ -582,8 +597,9 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                 for(int pi = 0; pi < sch.n; ++pi)
                 {
                     const WsPiece pc = sch.piece(pi);
+                    const int     mat = pc.tile_id / tiles_per_matrix;
                     int           tile_m, tile_n;
-                    map_tile<Cfg::RASTER>(pc.tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
+                    map_tile<Cfg::RASTER>(pc.tile_id - mat * tiles_per_matrix, p.grid_m, p.grid_n, tile_m, tile_n);
                     const int m0 = tile_m * BM, n0 = tile_n * BN;
                     const int ntiles = (pc.k_end - pc.k_begin + BK - 1) / BK;
                     for(int t = 0; t < ntiles; ++t)
@@ -598,9 +614,9 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                         }
                         mbar_arrive_expect_tx(sfull_bar(j), staged_bytes);
                         if(stg_a)
-                            tma_load_3d(smem_u32(slot_a(j)), &map_a, k0, m0 >> 2, 0, sfull_bar(j));
+                            tma_load_4d(smem_u32(slot_a(j)), &map_a, k0, m0 >> 2, 0, mat * w.bstep_a, sfull_bar(j));
                         if(stg_b)
-                            tma_load_3d(smem_u32(slot_b(j)), &map_b, k0, n0 >> 2, 0, sfull_bar(j));
+                            tma_load_4d(smem_u32(slot_b(j)), &map_b, k0, n0 >> 2, 0, mat * w.bstep_b, sfull_bar(j));
                         if(direct_bytes)
                         {
                             if(!mbar_wait_parked(empty_bar(s), phase ^ 1u, abort_flag))
@@ -610,9 +626,9 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                             }
                             mbar_arrive_expect_tx(full_bar(s), direct_bytes);
                             if(w.tma_a)
-                                tma_load_2d(smem_u32(tile_a(s)), &map_a, m0, k0, full_bar(s));
+                                tma_load_3d(smem_u32(tile_a(s)), &map_a, m0, k0, mat * w.bstep_a, full_bar(s));
                             if(w.tma_b)
-                                tma_load_2d(smem_u32(tile_b(s)), &map_b, n0, k0, full_bar(s));
+                                tma_load_3d(smem_u32(tile_b(s)), &map_b, n0, k0, mat * w.bstep_b, full_bar(s));
                         }
                         if(++s == STAGES) { s = 0; phase ^= 1u; }
                         if(++j == L::STG_SLOTS) { j = 0; jphase ^= 1u; }
@@ -635,13 +651,16 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
         sch.init(w, tiles, BK);
         for(int pi = 0; pi < sch.n; ++pi)
         {
-            const WsPiece pc = sch.piece(pi);
+            const WsPiece pc  = sch.piece(pi);
+            const int     mat = pc.tile_id / tiles_per_matrix;
             int           tile_m, tile_n;
-            map_tile<Cfg::RASTER>(pc.tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
+            map_tile<Cfg::RASTER>(pc.tile_id - mat * tiles_per_matrix, p.grid_m, p.grid_n, tile_m, tile_n);
             const int m0 = tile_m * BM, n0 = tile_n * BN;
             const int k_begin = pc.k_begin;
             const int k_end   = pc.k_end;
             const int ntiles  = (k_end - k_begin + BK - 1) / BK;
+            const float* mat_a = p.A + mat * w.stride_a;
+            const float* mat_b = p.B + mat * w.stride_b;
             for(int t = 0; t < ntiles; ++t)
             {
                 // the stage was released `phase` laps ago; the very first lap passes immediately
@@ -665,9 +684,9 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                         mbar_arrive_expect_tx(full_bar(s), tx_bytes);
                         // tile origins are multiples of 32 elements: TMA's 16-byte start rule holds
                         if(w.tma_a)
-                            tma_load_2d(smem_u32(tile_a(s)), &map_a, m0, k0, full_bar(s));
+                            tma_load_3d(smem_u32(tile_a(s)), &map_a, m0, k0, mat * w.bstep_a, full_bar(s));
                         if(w.tma_b)
-                            tma_load_2d(smem_u32(tile_b(s)), &map_b, n0, k0, full_bar(s));
+                            tma_load_3d(smem_u32(tile_b(s)), &map_b, n0, k0, mat * w.bstep_b, full_bar(s));
                     }
                     else
                     {
@@ -675,9 +694,9 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     }
                 }
                 if(manual_a)
-                    stage_a.fetch(p.A, p.lda, p.M, m0, k0, k_end, p.vec_a, tile_a(s), ptid);
+                    stage_a.fetch(mat_a, p.lda, p.M, m0, k0, k_end, p.vec_a, tile_a(s), ptid);
                 if(manual_b)
-                    stage_b.fetch(p.B, p.ldb, p.N, n0, k0, k_end, p.vec_b, tile_b(s), ptid);
+                    stage_b.fetch(mat_b, p.ldb, p.N, n0, k0, k_end, p.vec_b, tile_b(s), ptid);
                 if(manual_a)
                     stage_a.commit(tile_a(s), ptid);
                 if(manual_b)
@@ -751,9 +770,10 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     constexpr int ACC_VEC = TMT * TNT / 4;
     for(int pi = 0; pi < sch.n; ++pi)
     {
-        const WsPiece pc = sch.piece(pi);
+        const WsPiece pc  = sch.piece(pi);
+        const int     mat = pc.tile_id / tiles_per_matrix;
         int           tile_m, tile_n;
-        map_tile<Cfg::RASTER>(pc.tile_id, p.grid_m, p.grid_n, tile_m, tile_n);
+        map_tile<Cfg::RASTER>(pc.tile_id - mat * tiles_per_matrix, p.grid_m, p.grid_n, tile_m, tile_n);
         const int m0 = tile_m * BM, n0 = tile_n * BN;
         const int k_begin = pc.k_begin;
         const int k_end   = pc.k_end;
@@ -1012,7 +1032,7 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                 d[0] = sum.x + d[0]; d[1] = sum.y + d[1]; d[2] = sum.z + d[2]; d[3] = sum.w + d[3];
             }
         }
-        store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)pc.split * p.split_stride, m0 + tm0, n0 + tn0);
+        store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)pc.split * p.split_stride + mat * w.stride_c, m0 + tm0, n0 + tn0);
         for(int d = 0; d < w.n_extra; ++d) // plain stores; to a peer GPU's memory when the pointer is a peer mapping
             store_tile<Cfg, LC, ALIGNED>(c, p, w.extra_c[d], m0 + tm0, n0 + tn0);
     }

@@ -147,3 +147,38 @@ def test_multi_destination_store(sgemm, orc, lc):
         sgemm.gemm_multi(lc, la, lb, [], dev(A), dev(B), M, n, K, ldc=ld)
     with pytest.raises(sgemm.SgemmError):
         sgemm.gemm_multi(lc, la, lb, [dsts[0]] * 9, dev(A), dev(B), M, n, K, ldc=ld)
+
+
+@pytest.mark.parametrize("layout", [(0, 0, 0), (1, 0, 0), (0, 1, 1), (1, 1, 0)], ids=lambda l: layout_name(*l))
+@pytest.mark.parametrize("case", [(512, 384, 256, 8, 0), (320, 512, 130, 5, 0), (256, 256, 512, 37, 0), (200, 136, 132, 6, 3)],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_strided_batched_one_launch(sgemm, orc, case, layout):
+    """Batches large enough to be worth one launch: the persistent CTAs walk the tiles of all matrices (with the
+    hand-over schedule when batch x tiles exceeds the SMs).  Every matrix must be the oracle's single FMA chain, bit
+    for bit; `pad` > 0 makes the strides odd, which sends the operands through the kernel's guarded route."""
+    (M, N, K, batch, pad), (la, lb, lc) = case, layout
+    sa, sb, sc = M * K + pad, K * N + pad, M * N + pad
+    hostA = np.zeros(batch * sa, dtype=np.float32)
+    hostB = np.zeros(batch * sb, dtype=np.float32)
+    A0, B0 = orc.fill_ab(50, la, lb, M, N, K)
+    rng = np.random.default_rng(51)
+    mats = []
+    for b in range(batch):
+        A = (A0 * np.float32(1 + 0.125 * b)).astype(np.float32) if b % 2 else rng.uniform(-1, 1, M * K).astype(np.float32)
+        B = B0 if b % 3 else rng.uniform(-1, 1, K * N).astype(np.float32)
+        hostA[b * sa:b * sa + M * K] = A
+        hostB[b * sb:b * sb + K * N] = B
+        mats.append((A, B))
+    dA, dB = dev(hostA), dev(hostB)
+    dC = torch.full((batch * sc,), float("nan"), device="cuda")
+    sgemm.gemm_strided_batched(lc, la, lb, dC, dA, dB, M, N, K, sc, sa, sb, batch)
+    torch.cuda.synchronize()
+    C = dC.cpu().numpy()
+    for b in (0, 1, batch // 2, batch - 1):
+        A, B = mats[b]
+        want = chain(sgemm, orc, lc, la, lb, A, B, M, N, K)
+        assert np.array_equal(bits(C[b * sc:b * sc + M * N]), bits(want)), b
+    if pad:
+        for b in range(batch):
+            assert np.isnan(C[b * sc + M * N:(b + 1) * sc]).all()
+    assert sgemm.device_status() == 0

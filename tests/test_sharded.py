@@ -61,6 +61,13 @@ def _worker(rank, world, port, results):
             def gemm(lc_, la_, lb_, C_, A_, B_, M_, N_, K_):
                 C_.copy_(torch.from_numpy(oracle.sgemm_fma(lc_, la_, lb_, A_.numpy(), B_.numpy(), M_, N_, K_)))
 
+            # the host pipeline's upload rule: each rank holds 1/G of the packed A, an in-place all-gather rebuilds it
+            off, cnt = sharded.a_upload_slice(la, M, K, world, rank)
+            dA = torch.zeros(M * K, dtype=torch.float32)
+            dA[off:off + cnt] = torch.from_numpy(A)[off:off + cnt]
+            parts = [torch.empty(cnt, dtype=torch.float32) for _ in range(world)]
+            dist.all_gather(parts, dA[off:off + cnt].clone())
+            ok = ok and np.array_equal(torch.cat(parts).numpy().view(np.uint32), A.view(np.uint32))
             sharded.sharded_gemm(gemm, lc, la, lb, Cl, torch.from_numpy(A), Bl, M, N, K, world, rank)
             full = sharded.all_gather_c(Cl, lc, M, N, world).numpy()
             want = oracle.sgemm_fma(lc, la, lb, A, B, M, N, K)
@@ -99,3 +106,19 @@ def test_block_offset_matches_assembly():
                 full[off + o * ld: off + o * ld + view.shape[1]] = view[o]
         want = sharded.assemble_c(torch.cat(blocks), lc, M, N, world)
         assert torch.equal(full, want)
+
+
+def test_a_upload_slices_tile_the_operand():
+    from rocm_sgemm_b200 import sharded
+    M, K = 16, 24
+    for world in (1, 2, 4, 8):
+        seen = np.zeros(M * K, dtype=np.int32)
+        for r in range(world):
+            off, cnt = sharded.a_upload_slice(0, M, K, world, r)
+            assert cnt == M * K // world
+            seen[off:off + cnt] += 1
+        assert (seen == 1).all()
+    with pytest.raises(ValueError):
+        sharded.a_upload_slice(0, 3, 5, 2, 0)
+    with pytest.raises(ValueError):
+        sharded.a_upload_slice(0, 4, 4, 2, 2)

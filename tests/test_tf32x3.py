@@ -88,3 +88,26 @@ def test_argument_errors(sgemm):
         sgemm.gemm_3xtf32(0, 0, 2, A, A, A, 4, 4, 4)
     with pytest.raises(sgemm.SgemmError):
         sgemm.gemm_3xtf32(0, 0, 0, None, A, A, 4, 4, 4)
+
+
+def test_two_streams(sgemm):
+    """Calls that repack their operands (col-major A, row-major B) on two streams at once: each stream has its own
+    repack scratch, so the results are those of the same calls made one after the other, bit for bit."""
+    shapes = [(1536, 1280, 1024), (1280, 1536, 768)]
+    g = torch.Generator(device="cuda").manual_seed(25)
+    ops = []
+    for (M, N, K) in shapes:
+        A = torch.rand(M * K, device="cuda", generator=g) * 2 - 1
+        B = torch.rand(K * N, device="cuda", generator=g) * 2 - 1
+        alone = torch.empty(M * N, device="cuda")
+        sgemm.gemm_3xtf32(0, 1, 0, alone, A, B, M, N, K)  # crr: both operands are repacked
+        torch.cuda.synchronize()
+        ops.append((M, N, K, A, B, alone, torch.full((M * N,), float("nan"), device="cuda")))
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for _ in range(6):  # interleaved submissions, so that the two streams' kernels overlap on the GPU
+        for s, (M, N, K, A, B, _, C) in zip(streams, ops):
+            sgemm.gemm_3xtf32(0, 1, 0, C, A, B, M, N, K, stream=s)
+    torch.cuda.synchronize()
+    for (_, _, _, _, _, alone, C) in ops:
+        assert torch.equal(C.view(torch.int32), alone.view(torch.int32))
+    assert sgemm.tf32x3_device_status() == 0
