@@ -199,8 +199,12 @@ int b200_sgemm_shutdown_host(void);
 /* The same product for `batch` matrices at fixed element strides: matrix b uses C + b*stride_c, A + b*stride_a,
  * B + b*stride_b (stride_a or stride_b may be 0 to share an operand; the C matrices must not overlap).  The
  * reference's benchmark has a --batch_count switch that only replicates buffers
- * (benchmark/gemm/bench.cpp:49-64,213-216); this entry computes every matrix, one launch per matrix on the
- * stream, with the drop-in entry's table lookup and arena. */
+ * (benchmark/gemm/bench.cpp:49-64,213-216); this entry computes every matrix, with the drop-in entry's table
+ * lookup and arena.  Where the table's kernel for the problem is a warp-specialised one without K slices the whole
+ * batch is ONE launch: the persistent CTAs walk the tiles of all matrices (the batch is one more dimension of the
+ * tensor maps), so a batch of small problems fills the SMs; every matrix is then one FMA chain per element, with
+ * K-contiguous operands going through the kernel's staging ring and strides that are not multiples of 4 floats
+ * through its guarded route.  Otherwise: one launch per matrix on the stream. */
 int b200_sgemm_strided_batched(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
                                size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a, size_t stride_b,
                                size_t batch, void* cuda_stream);
