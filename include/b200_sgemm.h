@@ -200,11 +200,13 @@ int b200_sgemm_shutdown_host(void);
  * B + b*stride_b (stride_a or stride_b may be 0 to share an operand; the C matrices must not overlap).  The
  * reference's benchmark has a --batch_count switch that only replicates buffers
  * (benchmark/gemm/bench.cpp:49-64,213-216); this entry computes every matrix, with the drop-in entry's table
- * lookup and arena.  Where the table's kernel for the problem is a warp-specialised one without K slices the whole
- * batch is ONE launch: the persistent CTAs walk the tiles of all matrices (the batch is one more dimension of the
- * tensor maps), so a batch of small problems fills the SMs; every matrix is then one FMA chain per element, with
- * K-contiguous operands going through the kernel's staging ring and strides that are not multiples of 4 floats
- * through its guarded route.  Otherwise: one launch per matrix on the stream. */
+ * lookup and arena.  A batch (batch > 1) is ONE launch of a warp-specialised kernel: the persistent CTAs walk the
+ * tiles of all matrices (the batch is one more dimension of the tensor maps), so a batch of small problems fills the
+ * SMs.  The matrices are the parallel work, so a batch never slices K, whatever the table entry of the single
+ * problem says (an entry with K slices or a kernel of the other pipeline is replaced by a warp-specialised variant
+ * built for the layout): every matrix is one k-ascending FMA chain per element.  K-contiguous operands go through
+ * the kernel's staging ring and strides that are not multiples of 4 floats through its guarded route.  Only when
+ * no such kernel is built for the layout: one launch per matrix on the stream, each as b200_sgemm would run it. */
 int b200_sgemm_strided_batched(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
                                size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a, size_t stride_b,
                                size_t batch, void* cuda_stream);

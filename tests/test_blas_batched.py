@@ -15,8 +15,11 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def chain(sgemm, orc, lc, la, lb, A, B, M, N, K):
-    """The oracle's result with the split the table selects for this problem."""
+def chain(sgemm, orc, lc, la, lb, A, B, M, N, K, batch=1):
+    """The oracle's result with the split the table selects for this problem.  A batch never slices K (its matrices
+    are the parallel work): every matrix of a batch is one k-ascending FMA chain per element."""
+    if batch > 1:
+        return orc.sgemm_fma(lc, la, lb, A, B, M, N, K, splits=1, threads=orc.max_threads())
     from common import oracle_chain
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     return oracle_chain(sgemm, orc, la, lb, lc, A, B, M, N, K, sms)
@@ -41,7 +44,7 @@ def test_strided_batched(sgemm, orc, layout):
     torch.cuda.synchronize()
     C = dC.cpu().numpy()
     for b, (A, B) in enumerate(mats):
-        want = chain(sgemm, orc, lc, la, lb, A, B, M, N, K)
+        want = chain(sgemm, orc, lc, la, lb, A, B, M, N, K, batch)
         assert np.array_equal(bits(C[b * sc:b * sc + M * N]), bits(want)), b
         assert np.isnan(C[b * sc + M * N:(b + 1) * sc]).all()  # the padding between matrices is untouched
 
@@ -53,7 +56,7 @@ def test_strided_batched_shared_operand_and_errors(sgemm, orc):
     dC = torch.empty(batch * M * N, device="cuda")
     sgemm.gemm_strided_batched(0, 0, 0, dC, dA, dB, M, N, K, M * N, 0, K * N, batch)  # A shared (stride 0)
     torch.cuda.synchronize()
-    want = chain(sgemm, orc, 0, 0, 0, A, B, M, N, K)
+    want = chain(sgemm, orc, 0, 0, 0, A, B, M, N, K, batch)
     C = dC.cpu().numpy()
     for b in range(batch):
         assert np.array_equal(bits(C[b * M * N:(b + 1) * M * N]), bits(want))
@@ -176,7 +179,7 @@ def test_strided_batched_one_launch(sgemm, orc, case, layout):
     C = dC.cpu().numpy()
     for b in (0, 1, batch // 2, batch - 1):
         A, B = mats[b]
-        want = chain(sgemm, orc, lc, la, lb, A, B, M, N, K)
+        want = chain(sgemm, orc, lc, la, lb, A, B, M, N, K, batch)
         assert np.array_equal(bits(C[b * sc:b * sc + M * N]), bits(want)), b
     if pad:
         for b in range(batch):

@@ -16,20 +16,22 @@ from common import as2d, bits, layout_name, oracle_chain
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
-WS_VARIANT = None
+WS_VARIANTS = {}
 
 
-def ws_variant(sgemm):
-    """The 128 x 128 x 32 warp-specialised variant of the shipped table."""
-    global WS_VARIANT
-    if WS_VARIANT is None:
+def ws_variant(sgemm, la=0, lb=0, lc=0):
+    """A 128 x 128 x 32 warp-specialised variant of the shipped table that is built for this layout (variants are
+    compiled only for the layouts whose table entries name them)."""
+    key = (la, lb, lc)
+    if key not in WS_VARIANTS:
         for i in range(sgemm.num_variants()):
             p = sgemm.get_variant(i)
-            if (p.pipeline, p.block_m, p.block_n, p.block_k, p.block_size, p.raster) == (1, 128, 128, 32, 256, 1):
-                WS_VARIANT = i
+            if ((p.pipeline, p.block_m, p.block_n, p.block_k, p.block_size) == (1, 128, 128, 32, 256)
+                    and sgemm.has_kernel(i, la, lb, lc, True) and sgemm.has_kernel(i, la, lb, lc, False)):
+                WS_VARIANTS[key] = i
                 break
-    assert WS_VARIANT is not None
-    return WS_VARIANT
+    assert key in WS_VARIANTS, "no 128x128x32 warp-specialised kernel for layout %s" % (key,)
+    return WS_VARIANTS[key]
 
 
 def sms():
@@ -50,7 +52,7 @@ def run_ex(sgemm, la, lb, lc, A, B, M, N, K, variant, split_k, with_workspace=Tr
 @pytest.mark.parametrize("shape", [(2048, 2048, 256), (1664, 1920, 130), (2500, 1100, 96)], ids=lambda s: "x".join(map(str, s)))
 def test_handover_schedule_is_the_single_chain(sgemm, orc, shape, layout):
     (M, N, K), (la, lb, lc) = shape, layout
-    v = ws_variant(sgemm)
+    v = ws_variant(sgemm, la, lb, lc)
     A, B = orc.fill_ab(41, la, lb, M, N, K)
     got, nbytes = run_ex(sgemm, la, lb, lc, A, B, M, N, K, v, 1)
     assert nbytes > 0, "more tiles than SMs and a ragged last wave: the schedule must apply"
@@ -66,7 +68,7 @@ def test_handover_schedule_is_the_single_chain(sgemm, orc, shape, layout):
                          ids=lambda s: "x".join(map(str, s)))
 def test_equal_ranges_schedule(sgemm, orc, shape, layout):
     (M, N, K), (la, lb, lc) = shape, layout
-    v = ws_variant(sgemm)
+    v = ws_variant(sgemm, la, lb, lc)
     A, B = orc.fill_ab(43, la, lb, M, N, K)
     got, nbytes = run_ex(sgemm, la, lb, lc, A, B, M, N, K, v, -1)
     blk, offs, bnd = sgemm.stream_plan(lc, la, lb, M, N, K, v, -1, sms())
