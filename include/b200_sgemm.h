@@ -105,8 +105,8 @@ int b200_sgemm_multi(int layout_c, int layout_a, int layout_b, float* const* C_l
 
 /* The K cut points of the "equal ranges" schedule (split_k -1 in b200_sgemm_ex, split_k 0 in a table entry) for
  * a problem on a device with sm_count SMs, so that a host-side check can restate the arithmetic: every tile's K
- * extent is cut at the reported points, each piece is a k-ascending FMA chain from zero, and C is the sum of the
- * pieces in ascending K order.  Tiles are block_mnk[0] x block_mnk[1] (block_mnk[2] = the K tile), numbered
+ * extent is cut at the reported points, each piece is a k-ascending FMA chain from zero, and C is the last piece's
+ * chain plus the earlier pieces, added one by one in ascending K order: ((p_last + p_0) + p_1) + ...  Tiles are block_mnk[0] x block_mnk[1] (block_mnk[2] = the K tile), numbered
  * tile_row * ceil(N / block_n) + tile_column; offsets[t] .. offsets[t+1] index tile t's cut points in `bounds` (K
  * positions strictly between 0 and K).  Returns the total number of cut points (0 = this call would not use the
  * schedule: no cuts at all, or equal slices), negative = error; at most `capacity` entries of either array are

@@ -127,7 +127,7 @@ def sgemm_fma(lc, la, lb, A, B, M, N, K, rows=None, splits=1, k_align=1, threads
 
 
 def sgemm_fma_pieces(lc, la, lb, A, B, M, N, K, block_m, block_n, offsets, bounds, rows=None, threads=1) -> np.ndarray:
-    """FMA chains with per-tile K cut points, added in ascending K order (offsets / bounds as returned by the
+    """FMA chains with per-tile K cut points: the last piece's chain plus the earlier pieces in ascending K order (offsets / bounds as returned by the
     library's stream_plan: offsets has tiles + 1 entries, tile = tile_row * ceil(N / block_n) + tile_column)."""
     C = np.zeros(M * N, dtype=np.float32)
     r0, r1 = _band(M, rows)

@@ -207,7 +207,8 @@ void oracle_sgemm_fma(int lc, int la, int lb, float* C, const float* A, const fl
 /* The same chains with tile-dependent K cut points (the schedule that cuts the tiles' K extents into equal ranges
  * per CTA): C(i,j) belongs to tile (i / block_m) * ceil(N / block_n) + j / block_n, whose cut points are
  * bounds[offsets[t] .. offsets[t+1]) (ascending, strictly between 0 and K).  Every piece is a k-ascending fmaf chain
- * from zero and the pieces are added in ascending K order: total = ((p0 + p1) + p2) + ...
+ * from zero; the owner of the tile's last piece adds the earlier pieces to its own chain in ascending K order:
+ * total = ((p_last + p0) + p1) + ...  (with two pieces that is p0 + p1 either way: float addition commutes).
  * (The reference's kernel, kernel/kernel.hpp:188-266, is the single-piece case.) */
 void oracle_sgemm_fma_pieces(int lc, int la, int lb, float* C, const float* A, const float* B, size_t M, size_t N,
                              size_t K, size_t row_begin, size_t row_end, size_t block_m, size_t block_n,
@@ -223,16 +224,19 @@ void oracle_sgemm_fma_pieces(int lc, int la, int lb, float* C, const float* A, c
         {
             const size_t t     = (i / block_m) * grid_n + j / block_n;
             const int    first = offsets[t], last = offsets[t + 1];
-            float        total = 0.0f;
-            size_t       k0    = 0;
-            for(int piece = first; piece <= last; ++piece)
+            /* the last piece first: it is the chain the other pieces are added to */
+            float total = 0.0f;
+            for(size_t k = last > first ? (size_t)bounds[last - 1] : 0; k < K; ++k)
+                total = fmaf(A[idx(la, M, K, i, k)], B[idx(lb, K, N, k, j)], total);
+            size_t k0 = 0;
+            for(int piece = first; piece < last; ++piece)
             {
-                const size_t k1  = piece < last ? (size_t)bounds[piece] : K;
+                const size_t k1  = (size_t)bounds[piece];
                 float        acc = 0.0f;
                 for(size_t k = k0; k < k1; ++k)
                     acc = fmaf(A[idx(la, M, K, i, k)], B[idx(lb, K, N, k, j)], acc);
-                total = (piece == first) ? acc : total + acc;
-                k0    = k1;
+                total += acc;
+                k0 = k1;
             }
             C[idx(lc, M, N, i, j)] = total;
         }

@@ -100,6 +100,9 @@ struct WsArgs
     float*    handover; // gridDim.x slots of block_m x block_n floats: slot c holds what CTA c parked
     unsigned* flags;    // one word per (CTA, consumer warp): == epoch once that warp's part of slot c is complete
     unsigned  epoch;    // differs from launch to launch, so the words never need clearing
+    // schedules 1 and 2: the units cut into ranges, (tiles - rr_tiles) * k_tiles = range_q * gridDim.x + range_r
+    long long range_q;
+    unsigned  range_r;
     // Batch of equal problems at fixed element strides (batch 1: one problem).  The tile sequence of all schedules is
     // then batch x (grid_m x grid_n) long: tile id = matrix * tiles_per_matrix + tile.  The tensor maps carry the
     // batch as one more dimension; bstep_a / bstep_b are 0 for an operand that all problems share.
@@ -126,6 +129,30 @@ struct WsPiece
 __host__ __device__ inline long long ws_range_begin(long long units, int ctas, int c)
 {
     return units * c / ctas;
+}
+
+// The same value from units = q * ctas + r (q, r from the host): q * c + floor(r * c / ctas).  r * c stays below
+// ctas^2, so the device divides 32-bit numbers instead of 64-bit ones (the schedule is set up before the first copy
+// can be issued: its arithmetic is on the critical path of a short kernel).
+__device__ __forceinline__ long long ws_range_begin_qr(long long q, unsigned r, unsigned ctas, unsigned c)
+{
+    return q * (long long)c + (long long)(ctas < 65536u ? (r * c) / ctas : (unsigned)(((unsigned long long)r * c) / ctas));
+}
+// floor and remainder of u / kts, with 32-bit division when u fits
+__device__ __forceinline__ void ws_divmod(long long u, int kts, int& quo, int& rem)
+{
+    if(u <= 0x7fffffffLL)
+    {
+        const unsigned uu = (unsigned)u;
+        quo = (int)(uu / (unsigned)kts);
+        rem = (int)(uu - (unsigned)quo * (unsigned)kts);
+    }
+    else
+    {
+        const long long x = u / kts;
+        quo = (int)x;
+        rem = (int)(u - x * kts);
+    }
 }
 
 // The list of pieces of this CTA, identical for its producer and consumer threads.
@@ -159,16 +186,17 @@ struct WsSchedule
         kts   = w.k_tiles;
         tile0 = sched == 1 ? w.rr_tiles : 0;
         n_rr  = tile0 / (int)gridDim.x;
-        const long long units = (long long)(tiles - tile0) * kts;
-        const long long u0    = ws_range_begin(units, gridDim.x, blockIdx.x);
-        const long long u1    = ws_range_begin(units, gridDim.x, blockIdx.x + 1);
+        const long long u0 = ws_range_begin_qr(w.range_q, w.range_r, gridDim.x, blockIdx.x);
+        const long long u1 = ws_range_begin_qr(w.range_q, w.range_r, gridDim.x, blockIdx.x + 1);
         park_tile = last_tile = -1;
         park_a = park_b = last_a = last_first = 0;
         whole0 = nwhole = 0;
         if(u1 > u0)
         {
-            const int x = (int)(u0 / kts), a = (int)(u0 - (long long)x * kts);       // first segment: tile x from a
-            const int y = (int)((u1 - 1) / kts), b = (int)(u1 - (long long)y * kts); // last segment: tile y up to b
+            int x, a, y, b;
+            ws_divmod(u0, kts, x, a);     // first segment: tile x from K tile a
+            ws_divmod(u1 - 1, kts, y, b); // last segment: tile y up to K tile b (exclusive)
+            b += 1;
             if(x == y)
             {
                 if(a == 0 && b == kts) { whole0 = x; nwhole = 1; }
@@ -186,7 +214,7 @@ struct WsSchedule
             {
                 // the owner of the first K tile of last_tile: walk down from the neighbour
                 int c = blockIdx.x - 1;
-                while(c > 0 && ws_range_begin(units, gridDim.x, c) > (long long)last_tile * kts)
+                while(c > 0 && ws_range_begin_qr(w.range_q, w.range_r, gridDim.x, c) > (long long)last_tile * kts)
                     --c;
                 last_first = c;
             }
@@ -768,6 +796,18 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     // parked accumulators: slot c is block_m x block_n floats, thread-major in 16-byte units so that the accesses of
     // a warp are contiguous; the reader is the thread with the same index in the next CTA
     constexpr int ACC_VEC = TMT * TNT / 4;
+    // A parked piece is published (fence + release of the warp's flag) one K tile into the next piece: by then the
+    // stores have long landed and the fence returns at once, instead of holding the warp until they are acknowledged.
+    int publish = -1;
+    auto publish_now = [&]() {
+        __syncwarp();
+        if(lane == 0)
+        {
+            __threadfence();
+            st_release_u32(w.flags + publish * CONSUMER_WARPS + warp_id, w.epoch);
+        }
+        publish = -1;
+    };
     for(int pi = 0; pi < sch.n; ++pi)
     {
         const WsPiece pc  = sch.piece(pi);
@@ -784,6 +824,8 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
         if(pc.recv >= 0)
         {
             // the chain of this tile was started by the previous CTA (first thing it did): take its accumulators over
+            if(publish >= 0)
+                publish_now(); // never wait for a neighbour while one's own piece is unpublished: the waits would chain
             const unsigned* flag = w.flags + pc.recv * CONSUMER_WARPS + warp_id;
             bool            got  = ld_acquire_u32(flag) == w.epoch;
             if(!got)
@@ -939,6 +981,8 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                 mbar_arrive(empty_bar(s)); // this warp is done reading stage s
             s     = s2;
             phase = phase2;
+            if(publish >= 0)
+                publish_now();
         }
         if(!ok)
         {
@@ -973,6 +1017,7 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
             // park the accumulators for the CTA that continues this tile, then publish them warp by warp (the reader
             // of a thread's values is the thread with the same index, so a warp only ever waits for its namesake and
             // no block-wide barrier is needed): the warp's stores -> __syncwarp -> one lane's gpu-scope release
+            // (at once when this was the CTA's last piece, else after the first K tile of the next piece)
             float4* dst = reinterpret_cast<float4*>(w.handover + (size_t)pc.send * (BM * BN)) + tid;
 #pragma unroll
             for(int v = 0; v < ACC_VEC; ++v)
@@ -980,18 +1025,15 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                 const float* q = &c[0][0] + 4 * v;
                 __stcg(dst + v * Cfg::BLOCK_SIZE, make_float4(q[0], q[1], q[2], q[3]));
             }
-            __syncwarp();
-            if(lane == 0)
-            {
-                __threadfence();
-                st_release_u32(w.flags + pc.send * CONSUMER_WARPS + warp_id, w.epoch);
-            }
-            continue;
+            publish = pc.send;
+            if(pi + 1 == sch.n)
+                publish_now();
+            continue; // parked
         }
         if(pc.reduce >= 0)
         {
-            // schedule 2: this CTA owns the last K range of the tile.  Total = ((p_first + p_next) + ...) + own, in
-            // ascending K order; each earlier piece was parked by its CTA before that CTA did anything else.
+            // schedule 2: this CTA owns the last K range of the tile.  Total = ((own + p_first) + p_next) + ..., the
+            // earlier pieces in ascending K order; each was parked by its CTA before that CTA did anything else.
             for(int src_cta = pc.reduce; src_cta < (int)blockIdx.x; ++src_cta)
             {
                 const unsigned* flag = w.flags + src_cta * CONSUMER_WARPS + warp_id;
@@ -1017,19 +1059,23 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     return;
                 }
             }
-            // all pieces are there: four accumulators at a time, so that only four partial sums are alive at once
+            // all pieces are there: add them to this CTA's own chain in ascending K order, one piece at a time with
+            // all of the piece's loads in flight together (the sum is ((own + p_first) + p_next) + ...)
             const float4* base = reinterpret_cast<const float4*>(w.handover) + tid;
-#pragma unroll
-            for(int v = 0; v < ACC_VEC; ++v)
+#pragma unroll 1 // (unrolled, the compiler spills registers)
+            for(int src_cta = pc.reduce; src_cta < (int)blockIdx.x; ++src_cta)
             {
-                float4 sum = __ldcg(base + (size_t)pc.reduce * (BM * BN / 4) + v * Cfg::BLOCK_SIZE);
-                for(int src_cta = pc.reduce + 1; src_cta < (int)blockIdx.x; ++src_cta)
+                const float4* src = base + (size_t)src_cta * (BM * BN / 4);
+                float4        q[ACC_VEC];
+#pragma unroll
+                for(int v = 0; v < ACC_VEC; ++v)
+                    q[v] = __ldcg(src + v * Cfg::BLOCK_SIZE);
+#pragma unroll
+                for(int v = 0; v < ACC_VEC; ++v)
                 {
-                    const float4 q = __ldcg(base + (size_t)src_cta * (BM * BN / 4) + v * Cfg::BLOCK_SIZE);
-                    sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+                    float* d = &c[0][0] + 4 * v;
+                    d[0] += q[v].x; d[1] += q[v].y; d[2] += q[v].z; d[3] += q[v].w;
                 }
-                float* d = &c[0][0] + 4 * v;
-                d[0] = sum.x + d[0]; d[1] = sum.y + d[1]; d[2] = sum.z + d[2]; d[3] = sum.w + d[3];
             }
         }
         store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)pc.split * p.split_stride + mat * w.stride_c, m0 + tm0, n0 + tn0);

@@ -111,11 +111,25 @@ def test_fma_pieces_restates_ordered_sum_of_chains(orc):
     tiles = 3 * 3
     none = orc.sgemm_fma_pieces(0, 0, 1, A, B, M, N, K, bm, bn, np.zeros(tiles + 1, np.int32), np.zeros(0, np.int32))
     assert np.array_equal(none.view(np.uint32), orc.sgemm_fma(0, 0, 1, A, B, M, N, K).view(np.uint32))
-    # slices of 48 in every tile = sgemm_fma(splits=3, k_align=16): [0,48) [48,96) [96,100)
+    # one cut at 64 in every tile = sgemm_fma(splits=2, k_align=16): [0,64) [64,100); two pieces commute
+    offs = np.arange(tiles + 1, dtype=np.int32)
+    bnd = np.full(tiles, 64, np.int32)
+    same = orc.sgemm_fma_pieces(0, 0, 1, A, B, M, N, K, bm, bn, offs, bnd)
+    assert np.array_equal(same.view(np.uint32), orc.sgemm_fma(0, 0, 1, A, B, M, N, K, splits=2, k_align=16).view(np.uint32))
+    # three pieces [0,48) [48,96) [96,100): the last piece's chain first, then the others in ascending K order
     offs = np.arange(tiles + 1, dtype=np.int32) * 2
     bnd = np.tile(np.array([48, 96], np.int32), tiles)
-    same = orc.sgemm_fma_pieces(0, 0, 1, A, B, M, N, K, bm, bn, offs, bnd)
-    assert np.array_equal(same.view(np.uint32), orc.sgemm_fma(0, 0, 1, A, B, M, N, K, splits=3, k_align=16).view(np.uint32))
+    three = orc.sgemm_fma_pieces(0, 0, 1, A, B, M, N, K, bm, bn, offs, bnd).reshape(M, N)
+    a2, b2 = A.reshape(M, K), B.reshape(N, K)  # A row-major, B col-major
+
+    def chain(i, j, k0, k1):
+        acc = np.float32(0)
+        for k in range(k0, k1):
+            acc = np.float32(np.float64(a2[i, k]) * np.float64(b2[j, k]) + np.float64(acc))
+        return acc
+    for i, j in [(0, 0), (31, 33), (95, 79), (40, 7)]:
+        want = np.float32(np.float32(chain(i, j, 96, K) + chain(i, j, 0, 48)) + chain(i, j, 48, 96))
+        assert three[i, j].view(np.uint32) == want.view(np.uint32)
     # only tile (1, 2) is cut, at k = 40: checked against a direct evaluation
     offs = np.zeros(tiles + 1, np.int32)
     offs[1 * 3 + 2 + 1:] = 1
