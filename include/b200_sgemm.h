@@ -82,8 +82,10 @@ int b200_sgemm_ex(int layout_c, int layout_a, int layout_b, float* C, const floa
 
 /* One tuning trial: exactly what b200_sgemm does for a problem whose table entry names this kernel variant,
  * split_k (1 = none, n >= 2 = n slices + reduction kernel, 0 = equal K ranges per CTA) and pretranspose bits
- * (bit 0 / 1: copy a K-contiguous A / B transposed into the arena first) - scratch from the library's arena, the
- * balanced schedules where they apply.  The tuner times candidates through this entry, so that every property of
+ * (bit 0 / 1: a K-contiguous A / B is multiplied from a transposed copy in the arena; the warp-specialised
+ * kernels make that copy themselves, block by block ahead of their own reads, and bit 2 of a trial asks for a
+ * transposition kernel in front of the product instead, which is also what the other kernels get) - scratch from
+ * the library's arena, the balanced schedules where they apply.  The tuner times candidates through this entry, so that every property of
  * a table entry is searched through the path the drop-in entry takes; the reference's tuner launches its
  * JIT-compiled instantiation directly (rocm_sgemm/config/tuner.cpp:419-429). */
 int b200_sgemm_trial(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M,

@@ -75,6 +75,12 @@ extern "C" int b200_sgemm_selftest_bounded_wait(float* C, const float* A, const 
     w.k_tiles = K / Cfg::BK;
     w.test_omit_last_fill = 1;
     w.batch = 1;
+    w.coop_src_a = w.coop_src_b = nullptr;
+    w.coop_ld_a = w.coop_ld_b = 0;
+    w.coop_flags = nullptr;
+    w.coop_done = nullptr;
+    w.range_q = 0;
+    w.range_r = 0;
     CUtensorMap map_a, map_b;
     w.tma_a = encode(&map_a, A, M, K, Cfg::BM, Cfg::BK);
     w.tma_b = encode(&map_b, B, N, K, Cfg::BN, Cfg::BK);

@@ -78,6 +78,7 @@ constexpr uint64_t WS_WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull; // one second
 constexpr int WS_ERR_FULL_TIMEOUT  = 1; // a consumer gave up waiting for a stage to fill
 constexpr int WS_ERR_EMPTY_TIMEOUT = 2; // a producer gave up waiting for a stage to drain
 constexpr int WS_ERR_PEER_TIMEOUT  = 3; // a consumer gave up waiting for the neighbour CTA's parked accumulators
+constexpr int WS_ERR_COOP_TIMEOUT  = 4; // the copy-issuing thread gave up waiting for a block of a transposed operand
 
 struct WsArgs
 {
@@ -109,6 +110,18 @@ struct WsArgs
     int       batch;
     int       bstep_a, bstep_b;
     long long stride_a, stride_b, stride_c;
+    // In-kernel transposition of K-contiguous operands ("cooperative": every block is transposed once, by whichever
+    // CTA it falls to, for all CTAs that will read it).  coop_src_x != nullptr: g.A / g.B points at scratch memory that
+    // is to hold the operand as [K][X]; the producer warps that the TMA route leaves idle transpose it there from
+    // coop_src_x ([X rows][K], pitch coop_ld_x) in blocks of block_x rows x block_k columns, K tile by K tile, and
+    // publish each block through one word of coop_flags (== epoch: in place).  The thread that issues the TMA copies
+    // waits for the words of the two blocks a stage needs.  Block of A: word kt * XT + tile_m; block of B: word
+    // kt * XT + XA + tile_n, where XA = grid_m if A is transposed here (else 0) and XT = XA + (grid_n if B is).
+    const float* coop_src_a;
+    const float* coop_src_b;
+    long long    coop_ld_a, coop_ld_b;
+    unsigned*    coop_flags;
+    unsigned*    coop_done; // zero at launch; every transposing warp adds one when its last block is published
     // Self-test only (0 everywhere else): the thread that issues the TMA copies leaves out the very last K tile of its
     // last piece - no copy, no arrival - so the consumers' wait for that stage runs into its limit.
     int       test_omit_last_fill;
@@ -491,6 +504,56 @@ struct StagedTransposer
     }
 };
 
+// One block of the cooperative transposition, by one warp: rows [r0, r0 + BX) x columns [k0, k0 + BK) of src
+// ([X][K], pitch ld) -> dst ([K][X], pitch ldt).  A lane takes a 4 x 4 piece at a time: four 128-bit reads along k
+// (eight lanes cover 128 contiguous bytes of a row), a transposition in registers, four 128-bit writes along x (four
+// lanes cover 64 contiguous bytes).  X and K are multiples of 4, so a piece is entirely inside or outside.
+template<int BX, int BK>
+struct CoopTransposer
+{
+    static constexpr int G      = BX / 4;  // row groups of four
+    static constexpr int QK     = BK / 4;  // k quads of a block
+    static constexpr int GP     = 32 / QK; // row groups a warp covers per pass
+    static constexpr bool OK    = BK % 4 == 0 && QK <= 32 && 32 % QK == 0 && G % GP == 0;
+    static constexpr int PASSES = OK ? G / GP : 1;
+    static constexpr int BATCH  = PASSES % 8 == 0 ? 8 : PASSES % 4 == 0 ? 4 : PASSES % 2 == 0 ? 2 : 1; // pieces in flight per lane
+    static __device__ __forceinline__ void run(const float* __restrict__ src, long long ld, float* __restrict__ dst,
+                                               long long ldt, int X, int K, int r0, int k0, int lane)
+    {
+        const int  c  = lane % QK, gl = lane / QK;
+        const int  k  = k0 + 4 * c;
+        const bool k_ok = k < K;
+#pragma unroll 1
+        for(int pb = 0; pb < PASSES; pb += BATCH)
+        {
+            float4 r[BATCH][4];
+#pragma unroll
+            for(int b = 0; b < BATCH; ++b)
+            {
+                const int    x  = r0 + 4 * (gl + GP * (pb + b));
+                const bool   ok = k_ok && x < X;
+                const float* sp = src + (long long)x * ld + k;
+#pragma unroll
+                for(int i = 0; i < 4; ++i)
+                    r[b][i] = ok ? __ldcs(reinterpret_cast<const float4*>(sp + i * ld)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for(int b = 0; b < BATCH; ++b)
+            {
+                const int x = r0 + 4 * (gl + GP * (pb + b));
+                if(k_ok && x < X)
+                {
+                    float* dp = dst + (long long)k * ldt + x;
+                    *reinterpret_cast<float4*>(dp + 0 * ldt) = make_float4(r[b][0].x, r[b][1].x, r[b][2].x, r[b][3].x);
+                    *reinterpret_cast<float4*>(dp + 1 * ldt) = make_float4(r[b][0].y, r[b][1].y, r[b][2].y, r[b][3].y);
+                    *reinterpret_cast<float4*>(dp + 2 * ldt) = make_float4(r[b][0].z, r[b][1].z, r[b][2].z, r[b][3].z);
+                    *reinterpret_cast<float4*>(dp + 3 * ldt) = make_float4(r[b][0].w, r[b][1].w, r[b][2].w, r[b][3].w);
+                }
+            }
+        }
+    }
+};
+
 template<class Cfg, int LA, int LB, int LC, bool ALIGNED>
 __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     sgemm_ws_kernel(const __grid_constant__ WsArgs w, const __grid_constant__ CUtensorMap map_a,
@@ -526,6 +589,14 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
     auto tile_b = [&](int s) -> float* { return smem + s * L::STAGE_FLOATS + BM * BK; };
 
     const int tid = threadIdx.x;
+    if(tid == Cfg::BLOCK_SIZE)
+    {
+        // the thread that will issue the copies fetches the descriptors while thread 0 sets up the barriers
+        if(w.tma_a || w.stg_a)
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+        if(w.tma_b || w.stg_b)
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+    }
     if(tid == 0)
     {
         for(int s = 0; s < STAGES; ++s)
@@ -672,7 +743,48 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
         // Both operands by TMA: one thread does everything, the other producer threads leave at once.  (A warp
         // that merely polled a barrier would still take issue slots from the consumers on its scheduler.)
         if(!manual_a && !manual_b && ptid != 0)
+        {
+            // ---- cooperative transposition: the warps the TMA route leaves idle ---------------------------------
+            constexpr int COOP_WARPS = L::PRODUCERS / 32 - 1;
+            if constexpr(COOP_WARPS > 0 && CoopTransposer<BM, BK>::OK && CoopTransposer<BN, BK>::OK)
+            {
+                if(w.coop_flags && ptid >= 32)
+                {
+                    const int       lane_p = ptid & 31;
+                    const int       xa = w.coop_src_a ? p.grid_m : 0, xt = xa + (w.coop_src_b ? p.grid_n : 0);
+                    const long long units = (long long)w.k_tiles * xt;
+                    const long long step  = (long long)gridDim.x * COOP_WARPS;
+                    // blocks in the order the consumers need them (K tile by K tile), dealt round-robin to all warps
+                    for(long long u = (long long)blockIdx.x * COOP_WARPS + (ptid / 32 - 1); u < units; u += step)
+                    {
+                        const int kt = (int)(u / xt), x = (int)(u - (long long)kt * xt);
+
+                        if(x < xa)
+                            CoopTransposer<BM, BK>::run(w.coop_src_a, w.coop_ld_a, const_cast<float*>(p.A), p.lda, p.M,
+                                                        p.K, x * BM, kt * BK, lane_p);
+                        else
+                            CoopTransposer<BN, BK>::run(w.coop_src_b, w.coop_ld_b, const_cast<float*>(p.B), p.ldb, p.N,
+                                                        p.K, (x - xa) * BN, kt * BK, lane_p);
+                        __syncwarp(); // the warp's stores -> one lane's fence and gpu-scope release of the block's word
+                        if(lane_p == 0)
+                        {
+                            __threadfence();
+                            st_release_u32(w.coop_flags + u, w.epoch);
+                        }
+                    }
+                    if(lane_p == 0)
+                    {
+                        __threadfence(); // (a warp without blocks counts too)
+                        atomicAdd(w.coop_done, 1u);
+                    }
+                }
+            }
             return;
+        }
+        // words of the transposed blocks the copy-issuing thread has to see before it may fetch a stage
+        const int  coop_xa = w.coop_src_a ? p.grid_m : 0, coop_xt = coop_xa + (w.coop_src_b ? p.grid_n : 0);
+        bool       coop    = w.coop_flags != nullptr && !manual_a && !manual_b;
+        const unsigned coop_warps = gridDim.x * (unsigned)(L::PRODUCERS / 32 - 1);
         int      s     = 0; // ring position
         uint32_t phase = 0; // parity of the current lap
         WsSchedule sch;
@@ -707,6 +819,43 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     return; // self-test: this stage is never filled
                 if(ptid == 0)
                 {
+                    if(coop)
+                    {
+                        // the blocks of this stage must be in place (written by some CTA's transposing warps with
+                        // ordinary stores): acquire their words, then order those writes before the TMA reads
+                        const unsigned* fa = w.coop_flags + (long long)(k0 / BK) * coop_xt + (w.coop_src_a ? tile_m : 0);
+                        const unsigned* fb = w.coop_flags + (long long)(k0 / BK) * coop_xt + coop_xa + tile_n;
+                        if(!w.coop_src_a) fa = fb;
+                        if(!w.coop_src_b) fb = fa;
+                        // (both reads in flight together; every eighth stage also looks whether all warps have finished:
+                        // from then on nothing needs checking any more)
+                        const unsigned va = ld_acquire_u32(fa), vb = ld_acquire_u32(fb);
+                        bool           got = va == w.epoch && vb == w.epoch;
+                        if(got && (t & 7) == 0 && ld_acquire_u32(w.coop_done) == coop_warps)
+                            coop = false;
+                        if(!got)
+                        {
+                            const uint64_t t0 = global_timer_ns();
+                            for(uint32_t it = 0; it < WS_SPIN_LIMIT && !got; ++it)
+                            {
+                                __nanosleep(100);
+                                got = ld_acquire_u32(fa) == w.epoch && ld_acquire_u32(fb) == w.epoch;
+                                if(!got && (it & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > WS_WAIT_LIMIT_NS))
+                                    break;
+                            }
+                        }
+                        if(!got)
+                        {
+                            if(!*abort_flag)
+                            {
+                                *abort_flag = 1;
+                                atomicCAS(w.status, 0, WS_ERR_COOP_TIMEOUT);
+                            }
+                            __nanosleep(200000); // let copies already in flight land before the CTA retires
+                            return;
+                        }
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                    }
                     if(tx_bytes)
                     {
                         mbar_arrive_expect_tx(full_bar(s), tx_bytes);

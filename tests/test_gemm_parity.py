@@ -458,3 +458,39 @@ def test_bounded_wait_gives_up_and_reports(sgemm):
     ref = dA.view(64, 128).T.double() @ dB.view(64, 128).double()
     assert float((dC.view(128, 128).double() - ref).abs().max()) < 1e-4
     assert sgemm.device_status() == 0
+
+
+@pytest.mark.parametrize("layout", [(0, 0, 0), (0, 1, 0), (1, 1, 1), (0, 1, 1)], ids=lambda l: layout_name(*l))
+@pytest.mark.parametrize("shape", [(1024, 1024, 512), (1028, 1100, 1036), (1152, 1026, 260)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_transposition_inside_the_kernel(sgemm, orc, shape, layout):
+    """Entries with pretranspose bits multiply a K-contiguous operand from a transposed copy.  The warp-specialised
+    kernels make that copy themselves (idle producer warps transpose it block by block, the copy-issuing thread
+    waits for the blocks a stage needs); bit 2 of a trial's pretranspose argument asks for the transposition kernel
+    in front of the product instead.  Both must give the oracle's single FMA chain bit for bit.  The second shape
+    has ragged tiles in every dimension; in the third N is not a multiple of 4, so a column-major B cannot be
+    transposed inside and the library falls back to the kernel in front by itself."""
+    (M, N, K), (la, lb, lc) = shape, layout
+    pre = (1 if la == 0 else 0) | (2 if lb == 1 else 0)
+    variant = None
+    for i in range(sgemm.num_variants()):
+        p = sgemm.get_variant(i)
+        if ((p.pipeline, p.block_m, p.block_n, p.block_k, p.block_size) == (1, 128, 128, 32, 256)
+                and all(sgemm.has_kernel(i, a, b, lc, al) for a, b in ((la, lb), (1, lb), (1, 0), (la, 0)) for al in (True, False))):
+            variant = i
+            break
+    if variant is None:
+        pytest.skip("no 128x128x32 warp-specialised variant built for this layout and its transposed forms")
+    A, B = orc.fill_ab(61, la, lb, M, N, K)
+    dA, dB = dev(A), dev(B)
+    got = []
+    for bits_ in (pre, pre | 4):
+        dC = torch.full((M * N,), float("nan"), dtype=torch.float32, device="cuda")
+        for _ in range(2):  # twice: the second call finds the flag words of the first (an older epoch)
+            sgemm.gemm_trial(lc, la, lb, dC, dA, dB, M, N, K, variant, 1, bits_)
+        torch.cuda.synchronize()
+        got.append(dC.cpu().numpy())
+    want = orc.sgemm_fma(lc, la, lb, A, B, M, N, K, splits=1, threads=orc.max_threads())
+    assert np.array_equal(bits(got[0]), bits(want))
+    assert np.array_equal(bits(got[1]), bits(want))
+    assert sgemm.device_status() == 0

@@ -73,7 +73,7 @@ def test_equal_ranges_schedule(sgemm, orc, shape, layout):
     got, nbytes = run_ex(sgemm, la, lb, lc, A, B, M, N, K, v, -1)
     blk, offs, bnd = sgemm.stream_plan(lc, la, lb, M, N, K, v, -1, sms())
     if offs is None:
-        # too little work to cut (fewer than 4 K tiles per extra CTA): the plain schedule, one chain
+        # too little work to cut (fewer than 2 K tiles per extra CTA): the plain schedule, one chain
         assert nbytes == 0
         want = orc.sgemm_fma(lc, la, lb, A, B, M, N, K, threads=orc.max_threads())
     else:
