@@ -48,7 +48,7 @@ typedef struct b200_sgemm_params
     int min_blocks;        /* CTAs per SM the register budget is sized for */
     int pipeline;          /* 0 every warp stages and computes, 1 warp-specialised (TMA / producer warps + mbarriers) */
     int split_k;           /* K slices chosen for the looked-up problem (1 = none) */
-    int pretranspose;      /* bit 0 / 1: b200_sgemm first copies a K-contiguous A / B into M / N-contiguous scratch */
+    int pretranspose;      /* bit 0 / 1: b200_sgemm multiplies a K-contiguous A / B from an M / N-contiguous copy in scratch */
 } b200_sgemm_params;
 
 /* C = A*B, C overwritten, packed matrices, asynchronous on `cuda_stream` (a cudaStream_t; NULL = the
@@ -61,8 +61,11 @@ typedef struct b200_sgemm_params
  * tiles do not fill the last wave), split-K partial sums where the tuned table still slices K, and, where the
  * table entry asks for it and the problem is large enough for it to pay (the other dimension >= 1024), the
  * transposed copy of a K-contiguous operand (row-major A, col-major B), so that the hot kernel can fetch it
- * straight with TMA: about 1 % extra time at 4096^3 instead of 3.5 % for the transposition inside the
- * kernel.  b200_sgemm_ex never copies an operand: it runs exactly the kernel it is told. */
+ * straight with TMA.  The warp-specialised kernels make that copy themselves, block by block ahead of their own
+ * reads (each block once for all CTAs, by producer warps that would otherwise idle); a transposition kernel in
+ * front of the product makes it where that does not apply.  About 0.8 % extra time per operand at 4096^3, instead
+ * of 3.5 % for transposing every tile where it is consumed.  b200_sgemm_ex never copies an operand: it runs
+ * exactly the kernel it is told. */
 int b200_sgemm(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M, size_t N,
                size_t K, void* cuda_stream);
 
@@ -163,7 +166,8 @@ int b200_sgemm_fma_peak(int mode, int iterations, float* elapsed_ms, double* flo
 
 /* Reads (and clears) the current device's kernel status word after synchronising the device:
  * 0 = no kernel reported a problem; 1 / 2 = a warp-specialised kernel gave up a bounded wait on a
- * shared-memory barrier (consumer / producer side) and its output is invalid.  Diagnostic only: the
+ * shared-memory barrier (consumer / producer side), 3 = on another CTA's parked accumulators, 4 = on a block of
+ * an operand that the kernel transposes itself; its output is then invalid.  Diagnostic only: the
  * reference has no counterpart because its kernel has no waits that could time out. */
 int b200_sgemm_device_status(int* status);
 
