@@ -198,8 +198,13 @@ int b200_sgemm_host_wait(long long ticket);
 /* The schedule the host-buffer entries use for an M x N x K problem on a device with sm_count SMs, without touching a
  * device: returns the number of strips of C (one GEMM each, in launch order) and writes the first `capacity` of them
  * as (first row, rows, first column, columns) into rects[4*i..] and their split-K factors into splits[i].  The
- * strips tile C exactly once.  Negative return = B200_SGEMM_INVALID_ARGUMENT. */
+ * strips tile C exactly once.  Negative return = B200_SGEMM_INVALID_ARGUMENT.
+ * b200_sgemm_host_plan is the schedule of a job that finds the pipeline empty (pieces of about 512 rows / columns:
+ * the first strip starts after a few megabytes, for the latency of a single call); _pipelined the one of a job
+ * submitted while another is still in flight (pieces of about 2048: every strip then has at least 148 tiles and runs
+ * at the full kernel's rate, so that a stream of jobs goes at the pace of the uploads). */
 int b200_sgemm_host_plan(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits, int capacity);
+int b200_sgemm_host_plan_pipelined(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits, int capacity);
 int b200_sgemm_shutdown_host(void);
 
 /* The same product for `batch` matrices at fixed element strides: matrix b uses C + b*stride_c, A + b*stride_a,

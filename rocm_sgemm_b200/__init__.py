@@ -86,6 +86,7 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_get_entry_pretranspose", "b200_sgemm_map_tile",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
            "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_host_submit", "b200_sgemm_host_wait", "b200_sgemm_host_plan",
+           "b200_sgemm_host_plan_pipelined",
            "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
            "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
@@ -119,6 +120,7 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_host_submit.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, ctypes.POINTER(ctypes.c_longlong)]
     l.b200_sgemm_host_wait.argtypes = [ctypes.c_longlong]
     l.b200_sgemm_host_plan.argtypes = [_sz, _sz, _sz, i, ctypes.POINTER(_sz), ctypes.POINTER(i), i]
+    l.b200_sgemm_host_plan_pipelined.argtypes = [_sz, _sz, _sz, i, ctypes.POINTER(_sz), ctypes.POINTER(i), i]
     l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_3xtf32.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _vp]
     l.b200_sgemm_multi.argtypes = [i, i, i, ctypes.POINTER(_vp), i, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, i, _vp]
@@ -250,13 +252,15 @@ def gemm_host_submit(layout_c, layout_a, layout_b, C, A, B, M: int, N: int, K: i
     return int(t.value)
 
 
-def host_plan(M: int, N: int, K: int, sm_count: int = 148) -> list:
-    """Strips of C the host-buffer entries compute, in launch order: [((r0, rows, c0, cols), split_k), ...]."""
-    n = lib().b200_sgemm_host_plan(M, N, K, sm_count, None, None, 0)
+def host_plan(M: int, N: int, K: int, sm_count: int = 148, pipelined: bool = False) -> list:
+    """Strips of C the host-buffer entries compute, in launch order: [((r0, rows, c0, cols), split_k), ...]; `pipelined`:
+    the coarser schedule of a job submitted while another one is in flight."""
+    fn = lib().b200_sgemm_host_plan_pipelined if pipelined else lib().b200_sgemm_host_plan
+    n = fn(M, N, K, sm_count, None, None, 0)
     if n < 0:
         raise SgemmError(n, status_string(n))
     rects, splits = (_sz * (4 * n))(), (ctypes.c_int * n)()
-    lib().b200_sgemm_host_plan(M, N, K, sm_count, rects, splits, n)
+    fn(M, N, K, sm_count, rects, splits, n)
     return [(tuple(rects[4 * i:4 * i + 4]), splits[i]) for i in range(n)]
 
 

@@ -102,10 +102,10 @@ cudaError_t copy_block(float* dst, const float* src, int layout, size_t rows, si
     return copy_rect(dst, src, rows, c0, cn, r0, rn, kind, s);
 }
 
-// Pieces of one dimension: at most MAX_PIECES, multiples of 128 (the CTA tile), about 512 or more each.
-void cut(size_t dim, size_t* piece, int* count)
+// Pieces of one dimension: at most MAX_PIECES, multiples of 128 (the CTA tile), about `about` or more each.
+void cut(size_t dim, size_t about, size_t* piece, int* count)
 {
-    size_t want = std::min<size_t>(MAX_PIECES, std::max<size_t>(1, dim / 512));
+    size_t want = std::min<size_t>(MAX_PIECES, std::max<size_t>(1, dim / about));
     size_t len  = (dim + want - 1) / want;
     len         = (len + 127) / 128 * 128;
     *piece      = len;
@@ -145,7 +145,12 @@ struct Plan
     size_t            pm = 0, pn = 0;
     std::vector<Step> steps;
 };
-Plan make_plan(size_t M, size_t N, size_t K, int sms)
+// Two granularities.  A job that finds the pipeline empty is cut finely (pieces of about 512 rows / columns): its
+// first strips start after a few megabytes and the call's latency is what counts.  A job submitted while another one
+// is still in flight is cut coarsely (about 2048): then the uploads are the pace-maker, its strips have at least 148
+// tiles each and run at the full kernel's rate - the fine strips (16 to 128 tiles, one launch each) together take
+// 3.0 ms of GPU time at 4096^3, more than the 2.4 ms of the uploads they should hide behind.
+Plan make_plan(size_t M, size_t N, size_t K, int sms, bool pipelined)
 {
     Plan p;
     p.big = M >= 1024 && N >= 1024 && K >= 1024;
@@ -154,8 +159,8 @@ Plan make_plan(size_t M, size_t N, size_t K, int sms)
     int nm = 1, nn = 1;
     if(p.big)
     {
-        cut(M, &p.pm, &nm);
-        cut(N, &p.pn, &nn);
+        cut(M, pipelined ? 2048 : 512, &p.pm, &nm);
+        cut(N, pipelined ? 2048 : 512, &p.pn, &nn);
     }
     size_t rows_done = 0, cols_done = 0;
     for(int k = 0; k < std::max(nm, nn); ++k)
@@ -230,7 +235,14 @@ extern "C" int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, 
 
     // Large problems run the table's kernel for big cubes on every strip; small ones (one piece per operand) the
     // table's kernel for their shape, unsplit.
-    Plan                     plan  = make_plan(M, N, K, x.sms);
+    Slot&      other     = x.slot[(x.next_ticket + 1) % SLOTS];
+    bool       pipelined = false;
+    if(other.busy && cudaEventQuery(other.done) == cudaErrorNotReady)
+    {
+        pipelined = true;
+        (void)cudaGetLastError(); // "not ready" is an answer, not an error: keep it out of later error checks
+    }
+    Plan                     plan  = make_plan(M, N, K, x.sms, pipelined);
     const std::vector<Step>& steps = plan.steps;
     const size_t             pm = plan.pm, pn = plan.pn;
     int                      variant = -1;
@@ -307,11 +319,13 @@ extern "C" int b200_sgemm_host_submit(int layout_c, int layout_a, int layout_b, 
     return B200_SGEMM_OK;
 }
 
-extern "C" int b200_sgemm_host_plan(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits, int capacity)
+namespace
+{
+int write_plan(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits, int capacity, bool pipelined)
 {
     if(M == 0 || N == 0 || K == 0 || sm_count < 1 || capacity < 0 || (capacity > 0 && (!rects || !splits)))
         return B200_SGEMM_INVALID_ARGUMENT;
-    const Plan p = make_plan(M, N, K, sm_count);
+    const Plan p = make_plan(M, N, K, sm_count, pipelined);
     int        n = 0;
     for(const Step& s : p.steps)
     {
@@ -328,6 +342,18 @@ extern "C" int b200_sgemm_host_plan(size_t M, size_t N, size_t K, int sm_count, 
         ++n;
     }
     return n;
+}
+} // namespace
+
+extern "C" int b200_sgemm_host_plan(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits, int capacity)
+{
+    return write_plan(M, N, K, sm_count, rects, splits, capacity, false);
+}
+
+extern "C" int b200_sgemm_host_plan_pipelined(size_t M, size_t N, size_t K, int sm_count, size_t* rects, int* splits,
+                                              int capacity)
+{
+    return write_plan(M, N, K, sm_count, rects, splits, capacity, true);
 }
 
 extern "C" int b200_sgemm_host_wait(long long ticket)

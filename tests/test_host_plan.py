@@ -10,10 +10,11 @@ SHAPES = [(4096, 4096, 4096), (1024, 1024, 1024), (1100, 1536, 1024), (2304, 128
           (5000, 1025, 3000), (1024, 9000, 1024), (130, 70, 33), (1, 1, 1), (1023, 4096, 4096), (4096, 4096, 1000)]
 
 
+@pytest.mark.parametrize("pipelined", [False, True], ids=["single", "pipelined"])
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
-def test_strips_tile_c_exactly_once(sgemm, shape):
+def test_strips_tile_c_exactly_once(sgemm, shape, pipelined):
     M, N, K = shape
-    plan = sgemm.host_plan(M, N, K, 148)
+    plan = sgemm.host_plan(M, N, K, 148, pipelined)
     cover = np.zeros((-(-M // 64), -(-N // 64)), dtype=np.int32)  # 64-granular is enough: strips start on multiples of 128
     for (r0, rn, c0, cn), split in plan:
         assert rn > 0 and cn > 0 and r0 + rn <= M and c0 + cn <= N
@@ -22,7 +23,18 @@ def test_strips_tile_c_exactly_once(sgemm, shape):
         cover[r0 // 64:-(-(r0 + rn) // 64), c0 // 64:-(-(c0 + cn) // 64)] += 1
     assert (cover == 1).all()
     big = M >= 1024 and N >= 1024 and K >= 1024
-    assert len(plan) == 1 if not big else 1 < len(plan) <= 15
+    if not big:
+        assert len(plan) == 1
+    elif not pipelined:
+        assert 1 < len(plan) <= 15
+    else:
+        assert 1 <= len(plan) <= 15 and len(plan) <= len(sgemm.host_plan(M, N, K, 148))
+
+
+def test_4096_cube_pipelined_schedule(sgemm):
+    """A job submitted while another is in flight: two pieces per operand, three strips of 256, 256 and 512 tiles."""
+    plan = sgemm.host_plan(4096, 4096, 4096, 148, pipelined=True)
+    assert plan == [((0, 2048, 0, 2048), 1), ((2048, 2048, 0, 2048), 1), ((0, 4096, 2048, 2048), 1)]
 
 
 def test_4096_cube_schedule(sgemm):
