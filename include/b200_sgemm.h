@@ -268,6 +268,12 @@ int b200_sgemm_3xtf32_shutdown(void);
 int b200_sgemm_splitk_static(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
                              size_t M, size_t N, size_t K, int split_k, void* cuda_stream);
 
+/* Frees the scratch arena that b200_sgemm keeps for (current device, this stream), after waiting for the work queued
+ * on the stream.  The arenas are keyed on the stream handle: call this before destroying a stream that the drop-in
+ * entry has been used on, otherwise its arena stays allocated until b200_sgemm_shutdown (and a later stream that gets
+ * the same handle value inherits it, which is harmless).  Unknown streams are not an error. */
+int b200_sgemm_release_stream(void* cuda_stream);
+
 /* Frees the internal split-K arenas of every device (optional; they are also freed at unload). */
 int b200_sgemm_shutdown(void);
 

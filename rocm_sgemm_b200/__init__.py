@@ -86,7 +86,7 @@ EXPORTS = ("b200_sgemm", "b200_sgemm_ex", "b200_sgemm_workspace_bytes", "b200_sg
            "b200_sgemm_get_entry_pretranspose", "b200_sgemm_map_tile",
            "b200_sgemm_has_kernel", "b200_sgemm_select_in_table", "b200_sgemm_fma_peak", "b200_sgemm_device_status",
            "b200_sgemm_splitk_static", "b200_sgemm_host", "b200_sgemm_host_submit", "b200_sgemm_host_wait", "b200_sgemm_host_plan",
-           "b200_sgemm_host_plan_pipelined",
+           "b200_sgemm_host_plan_pipelined", "b200_sgemm_release_stream",
            "b200_sgemm_shutdown_host", "b200_sgemm_shutdown",
            "b200_sgemm_status_string", "b200_sgemm_3xtf32", "b200_sgemm_3xtf32_device_status",
            "b200_sgemm_3xtf32_shutdown", "b200_sgemm_strided_batched", "b200_sgemm_blas",
@@ -120,6 +120,7 @@ def lib() -> ctypes.CDLL:
     l.b200_sgemm_host_submit.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, ctypes.POINTER(ctypes.c_longlong)]
     l.b200_sgemm_host_wait.argtypes = [ctypes.c_longlong]
     l.b200_sgemm_host_plan.argtypes = [_sz, _sz, _sz, i, ctypes.POINTER(_sz), ctypes.POINTER(i), i]
+    l.b200_sgemm_release_stream.argtypes = [ctypes.c_void_p]
     l.b200_sgemm_host_plan_pipelined.argtypes = [_sz, _sz, _sz, i, ctypes.POINTER(_sz), ctypes.POINTER(i), i]
     l.b200_sgemm_splitk_static.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, i, _vp]
     l.b200_sgemm_3xtf32.argtypes = [i, i, i, _vp, _vp, _vp, _sz, _sz, _sz, _vp]
@@ -363,6 +364,11 @@ def device_status() -> int:
     st = ctypes.c_int(0)
     _check(lib().b200_sgemm_device_status(ctypes.byref(st)))
     return st.value
+
+
+def release_stream(stream=None) -> None:
+    """Frees the drop-in entry's scratch arena of (current device, stream) after synchronising the stream."""
+    _check(lib().b200_sgemm_release_stream(_stream(stream)))
 
 
 def shutdown() -> None:

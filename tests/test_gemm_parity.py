@@ -494,3 +494,30 @@ def test_transposition_inside_the_kernel(sgemm, orc, shape, layout):
     assert np.array_equal(bits(got[0]), bits(want))
     assert np.array_equal(bits(got[1]), bits(want))
     assert sgemm.device_status() == 0
+
+
+def test_release_stream_frees_the_arena(sgemm, orc):
+    """b200_sgemm_release_stream: the scratch the drop-in entry keeps for a stream goes back to the device (seen in
+    cudaMemGetInfo), a stream the library has never seen is not an error, and the next call on the stream simply
+    allocates again and gives the same bits."""
+    M, N, K = 1024, 1024, 16384  # the tabled skinny problem: parking slots in the arena
+    A, B = orc.fill_ab(71, 0, 0, M, N, K)
+    dA, dB = dev(A), dev(B)
+    dC = torch.empty(M * N, dtype=torch.float32, device="cuda")
+    s = torch.cuda.Stream()
+    sgemm.release_stream(s)  # unknown stream
+    with torch.cuda.stream(s):
+        sgemm.gemm(0, 0, 0, dC, dA, dB, M, N, K, stream=s)
+    s.synchronize()
+    first = dC.clone()
+    held, _ = torch.cuda.mem_get_info()
+    sgemm.release_stream(s)
+    freed, _ = torch.cuda.mem_get_info()
+    assert freed - held >= 1024 * 1024  # at least the arena's flag words came back
+    dC.fill_(float("nan"))
+    with torch.cuda.stream(s):
+        sgemm.gemm(0, 0, 0, dC, dA, dB, M, N, K, stream=s)
+    s.synchronize()
+    assert torch.equal(dC.view(torch.int32), first.view(torch.int32))
+    sgemm.release_stream(s)
+    assert sgemm.device_status() == 0
