@@ -1,17 +1,21 @@
-// API breadth beside the drop-in entry, built on the public C ABI only (b200_sgemm / b200_sgemm_ex):
+// API breadth beside the drop-in entry, built on the public C ABI (b200_sgemm / b200_sgemm_ex) and two internal entries
+// of the dispatch (one launch for a batch, alpha / beta in the epilogue):
 //
 //   b200_sgemm_strided_batched  the same product for `batch` matrices at fixed element strides.  The reference's
 //                               benchmark carries a --batch_count switch that replicates its buffers
 //                               (benchmark/gemm/bench.cpp:49-64,213-216) but its kernel multiplies one matrix;
-//                               here every matrix of the batch is computed, one launch per matrix on the stream.
+//                               here every matrix of the batch is computed, all of them by one launch of a
+//                               warp-specialised kernel (one launch per matrix where none is built for the layout).
 //   b200_sgemm_blas             the vendor-BLAS calling convention: column-major C, op(A) / op(B) selected by
 //                               transpose flags, leading dimensions, alpha and beta.  With alpha = 1, beta = 0 it is
 //                               the argument mapping of rocblas_wrapper::gemm<TRANSPOSE_A, TRANSPOSE_B>
 //                               (rocblas_wrapper/src/gemm.cpp:45-60: lda = TA ? K : M, ldb = TB ? N : K, ldc = M) onto
-//                               this library's kernels.  Other alpha / beta: the product goes to a scratch matrix
-//                               and one HBM-bound pass forms C = alpha * (A B) + beta * C with three separately
-//                               rounded FP32 operations (product, product, sum; no contraction), so that a host
-//                               restatement reproduces it bit for bit.  beta = 0 never reads C.
+//                               this library's kernels.  Other alpha / beta: C = alpha * (A B) + beta * C with three
+//                               separately rounded FP32 operations (product, product, sum; no contraction), so that
+//                               a host restatement reproduces it bit for bit; beta = 0 never reads C.  The
+//                               warp-specialised kernels do it in their epilogue; where the table's kernel slices K
+//                               or is of the other pipeline, the product goes to a scratch matrix and one HBM-bound
+//                               pass forms C.
 #include "../../include/b200_sgemm.h"
 
 #include <cuda_runtime.h>
@@ -74,6 +78,10 @@ cudaError_t scratch_get(cudaStream_t stream, size_t bytes, void** out)
 }
 } // namespace
 
+extern "C" int b200_sgemm_ex_scaled(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
+                                    size_t M, size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant,
+                                    int split_k, void* workspace, size_t workspace_bytes, float alpha, float beta,
+                                    void* cuda_stream);
 extern "C" int b200_sgemm_batched_launch(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
                                          size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a, size_t stride_b,
                                          size_t batch, void* cuda_stream); // sgemm_api.cu (not part of the public header)
@@ -123,6 +131,22 @@ extern "C" int b200_sgemm_blas(int trans_a, int trans_b, size_t M, size_t N, siz
     const bool   plain  = alpha == 1.f && beta == 0.f;
     // the table's split-K needs a workspace; the scratch block holds [T (only when alpha/beta apply)][workspace]
     const size_t ws_bytes = b200_sgemm_workspace_bytes(B200_SGEMM_COL_MAJOR, la, lb, M, N, K, -1, 0);
+    if(!plain)
+    {
+        // first choice: alpha and beta applied in the kernel's epilogue, no scratch matrix and no second pass (the
+        // warp-specialised kernels without K slices; the call launches nothing when the table's kernel cannot)
+        void* wsp = nullptr;
+        if(ws_bytes > 0)
+        {
+            cudaError_t e = scratch_get(stream, ws_bytes, &wsp);
+            if(e != cudaSuccess)
+                return (int)e;
+        }
+        const int st = b200_sgemm_ex_scaled(B200_SGEMM_COL_MAJOR, la, lb, C, A, B, M, N, K, lda, ldb, ldc, -1, 0, wsp,
+                                            ws_bytes, alpha, beta, cuda_stream);
+        if(st != B200_SGEMM_NO_KERNEL)
+            return st;
+    }
     const size_t t_bytes  = plain ? 0 : (M * N * sizeof(float) + 255) / 256 * 256;
     char*        block    = nullptr;
     if(ws_bytes + t_bytes > 0)

@@ -417,11 +417,40 @@ __host__ __device__ __forceinline__ void map_tile(int tile_id, int grid_m, int g
 // sub-tiles repeat every SUB_M rows and SUB_N columns.  128-bit stores along C's contiguous dimension
 // (the reference stores scalars: kernel/kernel.hpp:299-361); guarded unless ALIGNED.
 // ------------------------------------------------------------------------------------------------
-template<class Cfg, int LC, bool ALIGNED>
+// SCALE: instead of the plain store, out = alpha * c (+ beta * out when beta != 0) with every operation rounded
+// separately (multiply, multiply, add: no contraction), the arithmetic of the vendor-BLAS convention's entry.
+template<class Cfg, int LC, bool ALIGNED, bool SCALE = false>
 __device__ __forceinline__ void store_tile(const float (&c)[Cfg::TMT][Cfg::TNT], const GemmArgs& p,
-                                           float* __restrict__ out, int m_base, int n_base)
+                                           float* __restrict__ out, int m_base, int n_base, float alpha = 1.f,
+                                           float beta = 0.f)
 {
     constexpr int TM = Cfg::TM, TN = Cfg::TN;
+    auto put4 = [&](float* dst, float x, float y, float z, float w) {
+        if constexpr(SCALE)
+        {
+            float4 o = make_float4(__fmul_rn(alpha, x), __fmul_rn(alpha, y), __fmul_rn(alpha, z), __fmul_rn(alpha, w));
+            if(beta != 0.f)
+            {
+                const float4 q = *reinterpret_cast<const float4*>(dst);
+                o.x = __fadd_rn(o.x, __fmul_rn(beta, q.x));
+                o.y = __fadd_rn(o.y, __fmul_rn(beta, q.y));
+                o.z = __fadd_rn(o.z, __fmul_rn(beta, q.z));
+                o.w = __fadd_rn(o.w, __fmul_rn(beta, q.w));
+            }
+            *reinterpret_cast<float4*>(dst) = o;
+        }
+        else
+            *reinterpret_cast<float4*>(dst) = make_float4(x, y, z, w);
+    };
+    auto put1 = [&](float* dst, float x) {
+        if constexpr(SCALE)
+        {
+            const float o = __fmul_rn(alpha, x);
+            *dst          = beta != 0.f ? __fadd_rn(o, __fmul_rn(beta, *dst)) : o;
+        }
+        else
+            *dst = x;
+    };
     if constexpr(LC == LAYOUT_ROW)
     {
 #pragma unroll
@@ -440,9 +469,8 @@ __device__ __forceinline__ void store_tile(const float (&c)[Cfg::TMT][Cfg::TNT],
                     {
 #pragma unroll
                         for(int v = 0; v < TN / 4; ++v)
-                            *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1], c[i][in * TN + 4 * v + 2],
-                                c[i][in * TN + 4 * v + 3]);
+                            put4(dst + 4 * v, c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1], c[i][in * TN + 4 * v + 2],
+                                 c[i][in * TN + 4 * v + 3]);
                     }
                     else if(m < p.M)
                     {
@@ -450,16 +478,15 @@ __device__ __forceinline__ void store_tile(const float (&c)[Cfg::TMT][Cfg::TNT],
                         {
 #pragma unroll
                             for(int v = 0; v < TN / 4; ++v)
-                                *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                    c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1], c[i][in * TN + 4 * v + 2],
-                                    c[i][in * TN + 4 * v + 3]);
+                                put4(dst + 4 * v, c[i][in * TN + 4 * v], c[i][in * TN + 4 * v + 1],
+                                     c[i][in * TN + 4 * v + 2], c[i][in * TN + 4 * v + 3]);
                         }
                         else
                         {
 #pragma unroll
                             for(int jj = 0; jj < TN; ++jj)
                                 if(n + jj < p.N)
-                                    dst[jj] = c[i][in * TN + jj];
+                                    put1(dst + jj, c[i][in * TN + jj]);
                         }
                     }
                 }
@@ -483,9 +510,8 @@ __device__ __forceinline__ void store_tile(const float (&c)[Cfg::TMT][Cfg::TNT],
                     {
 #pragma unroll
                         for(int v = 0; v < TM / 4; ++v)
-                            *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j], c[im * TM + 4 * v + 2][j],
-                                c[im * TM + 4 * v + 3][j]);
+                            put4(dst + 4 * v, c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j], c[im * TM + 4 * v + 2][j],
+                                 c[im * TM + 4 * v + 3][j]);
                     }
                     else if(n < p.N)
                     {
@@ -493,16 +519,15 @@ __device__ __forceinline__ void store_tile(const float (&c)[Cfg::TMT][Cfg::TNT],
                         {
 #pragma unroll
                             for(int v = 0; v < TM / 4; ++v)
-                                *reinterpret_cast<float4*>(dst + 4 * v) = make_float4(
-                                    c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j], c[im * TM + 4 * v + 2][j],
-                                    c[im * TM + 4 * v + 3][j]);
+                                put4(dst + 4 * v, c[im * TM + 4 * v][j], c[im * TM + 4 * v + 1][j],
+                                     c[im * TM + 4 * v + 2][j], c[im * TM + 4 * v + 3][j]);
                         }
                         else
                         {
 #pragma unroll
                             for(int ii = 0; ii < TM; ++ii)
                                 if(m + ii < p.M)
-                                    dst[ii] = c[im * TM + ii][j];
+                                    put1(dst + ii, c[im * TM + ii][j]);
                         }
                     }
                 }

@@ -122,6 +122,10 @@ struct WsArgs
     long long    coop_ld_a, coop_ld_b;
     unsigned*    coop_flags;
     unsigned*    coop_done; // zero at launch; every transposing warp adds one when its last block is published
+    // The epilogue stores alpha * (A B) + beta * C (three separately rounded operations, C read only when beta != 0).
+    // alpha = 1, beta = 0 everywhere except in the vendor-BLAS convention's entry, which uses other values only without
+    // K slices and without further destinations.
+    float alpha, beta;
     // Self-test only (0 everywhere else): the thread that issues the TMA copies leaves out the very last K tile of its
     // last piece - no copy, no arrival - so the consumers' wait for that stage runs into its limit.
     int       test_omit_last_fill;
@@ -1227,7 +1231,10 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                 }
             }
         }
-        store_tile<Cfg, LC, ALIGNED>(c, p, p.C + (long long)pc.split * p.split_stride + mat * w.stride_c, m0 + tm0, n0 + tn0);
+        // (one epilogue for both uses: alpha = 1, beta = 0 reproduce the plain store bit for bit - x * 1 is x - and a
+        // second, unscaled copy of it cost two of the larger kernels a register spill)
+        store_tile<Cfg, LC, ALIGNED, true>(c, p, p.C + (long long)pc.split * p.split_stride + mat * w.stride_c, m0 + tm0,
+                                           n0 + tn0, w.alpha, w.beta);
         for(int d = 0; d < w.n_extra; ++d) // plain stores; to a peer GPU's memory when the pointer is a peer mapping
             store_tile<Cfg, LC, ALIGNED>(c, p, w.extra_c[d], m0 + tm0, n0 + tn0);
     }
