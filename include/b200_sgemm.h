@@ -225,10 +225,13 @@ int b200_sgemm_strided_batched(int layout_c, int layout_a, int layout_b, float* 
 /* Vendor-BLAS calling convention on this library's kernels: column-major C (ldc >= M),
  * C = alpha * op(A) * op(B) + beta * C, op(X) = X or X^T by trans_x (0 / 1), A stored (trans_a ? K x M : M x K)
  * with lda, B stored (trans_b ? N x K : K x N) with ldb.  With alpha = 1 and beta = 0 this is the mapping of
- * rocblas_wrapper::gemm<TRANSPOSE_A, TRANSPOSE_B> (rocblas_wrapper/src/gemm.cpp:45-60) and runs exactly the
- * kernels of b200_sgemm_ex.  Otherwise the product goes to a per-(device, stream) scratch matrix and one more
- * pass forms fl(fl(alpha*t) + fl(beta*c)) per element (three FP32 roundings, no contraction; beta = 0 does not
- * read C).  b200_sgemm_blas_shutdown frees the scratch. */
+ * rocblas_wrapper::gemm<TRANSPOSE_A, TRANSPOSE_B> (rocblas_wrapper/src/gemm.cpp:45-60) and takes the path of
+ * b200_sgemm (table entry, arena scratch, transposed copies, balanced schedules) with leading dimensions.
+ * Otherwise every element is fl(fl(alpha*t) + fl(beta*c)) (three FP32 roundings, no contraction; beta = 0 does not
+ * read C), formed in the epilogue of the warp-specialised kernels: no extra pass (measured at 4096^3: alpha = 2,
+ * beta = 0 costs nothing, beta = 0.5 adds the read of C, 1 %).  Only where the table's kernel slices K or is of
+ * the other pipeline the product goes to a per-(device, stream) scratch matrix and one more pass forms C;
+ * b200_sgemm_blas_shutdown frees that scratch. */
 int b200_sgemm_blas(int trans_a, int trans_b, size_t M, size_t N, size_t K, float alpha, const float* A, size_t lda,
                     const float* B, size_t ldb, float beta, float* C, size_t ldc, void* cuda_stream);
 int b200_sgemm_blas_shutdown(void);

@@ -78,10 +78,9 @@ cudaError_t scratch_get(cudaStream_t stream, size_t bytes, void** out)
 }
 } // namespace
 
-extern "C" int b200_sgemm_ex_scaled(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
-                                    size_t M, size_t N, size_t K, size_t lda, size_t ldb, size_t ldc, int variant,
-                                    int split_k, void* workspace, size_t workspace_bytes, float alpha, float beta,
-                                    void* cuda_stream);
+extern "C" int b200_sgemm_arena_ld(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
+                                   size_t M, size_t N, size_t K, size_t lda, size_t ldb, size_t ldc,
+                                   const float* alpha_beta, void* cuda_stream);
 extern "C" int b200_sgemm_batched_launch(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B,
                                          size_t M, size_t N, size_t K, size_t stride_c, size_t stride_a, size_t stride_b,
                                          size_t batch, void* cuda_stream); // sgemm_api.cu (not part of the public header)
@@ -128,40 +127,22 @@ extern "C" int b200_sgemm_blas(int trans_a, int trans_b, size_t M, size_t N, siz
     if(lda < (trans_a ? K : M) || ldb < (trans_b ? N : K) || ldc < M)
         return B200_SGEMM_INVALID_ARGUMENT;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    const bool   plain  = alpha == 1.f && beta == 0.f;
-    // the table's split-K needs a workspace; the scratch block holds [T (only when alpha/beta apply)][workspace]
-    const size_t ws_bytes = b200_sgemm_workspace_bytes(B200_SGEMM_COL_MAJOR, la, lb, M, N, K, -1, 0);
-    if(!plain)
-    {
-        // first choice: alpha and beta applied in the kernel's epilogue, no scratch matrix and no second pass (the
-        // warp-specialised kernels without K slices; the call launches nothing when the table's kernel cannot)
-        void* wsp = nullptr;
-        if(ws_bytes > 0)
-        {
-            cudaError_t e = scratch_get(stream, ws_bytes, &wsp);
-            if(e != cudaSuccess)
-                return (int)e;
-        }
-        const int st = b200_sgemm_ex_scaled(B200_SGEMM_COL_MAJOR, la, lb, C, A, B, M, N, K, lda, ldb, ldc, -1, 0, wsp,
-                                            ws_bytes, alpha, beta, cuda_stream);
-        if(st != B200_SGEMM_NO_KERNEL)
-            return st;
-    }
-    const size_t t_bytes  = plain ? 0 : (M * N * sizeof(float) + 255) / 256 * 256;
-    char*        block    = nullptr;
-    if(ws_bytes + t_bytes > 0)
-    {
-        void*       p = nullptr;
-        cudaError_t e = scratch_get(stream, ws_bytes + t_bytes, &p);
-        if(e != cudaSuccess)
-            return (int)e;
-        block = static_cast<char*>(p);
-    }
-    float* T  = plain ? C : reinterpret_cast<float*>(block);
-    void*  ws = ws_bytes ? block + t_bytes : nullptr;
-    int    st = b200_sgemm_ex(B200_SGEMM_COL_MAJOR, la, lb, T, A, B, M, N, K, lda, ldb, plain ? ldc : M, -1, 0, ws, ws_bytes,
-                              cuda_stream);
-    if(st != B200_SGEMM_OK || plain)
+    if(alpha == 1.f && beta == 0.f)
+        return b200_sgemm_arena_ld(B200_SGEMM_COL_MAJOR, la, lb, C, A, B, M, N, K, lda, ldb, ldc, nullptr, cuda_stream);
+    // first choice: alpha and beta applied in the kernel's epilogue, no scratch matrix and no second pass (the
+    // warp-specialised kernels without K slices; the call launches nothing when the table's kernel cannot)
+    const float ab[2] = {alpha, beta};
+    int         st    = b200_sgemm_arena_ld(B200_SGEMM_COL_MAJOR, la, lb, C, A, B, M, N, K, lda, ldb, ldc, ab, cuda_stream);
+    if(st != B200_SGEMM_NO_KERNEL)
+        return st;
+    // otherwise: the product into a packed scratch matrix T, then one pass C = alpha * T + beta * C
+    void*       p = nullptr;
+    cudaError_t e = scratch_get(stream, M * N * sizeof(float), &p);
+    if(e != cudaSuccess)
+        return (int)e;
+    float* T = static_cast<float*>(p);
+    st       = b200_sgemm_arena_ld(B200_SGEMM_COL_MAJOR, la, lb, T, A, B, M, N, K, lda, ldb, M, nullptr, cuda_stream);
+    if(st != B200_SGEMM_OK)
         return st;
     const size_t total  = M * N;
     size_t       blocks = (total + 255) / 256;
