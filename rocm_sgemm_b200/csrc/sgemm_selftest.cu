@@ -79,6 +79,7 @@ extern "C" int b200_sgemm_selftest_bounded_wait(float* C, const float* A, const 
     w.coop_ld_a = w.coop_ld_b = 0;
     w.coop_flags = nullptr;
     w.coop_done = nullptr;
+    w.coop_done_target = 0;
     w.alpha = 1.f;
     w.beta = 0.f;
     w.range_q = 0;

@@ -121,7 +121,11 @@ struct WsArgs
     const float* coop_src_b;
     long long    coop_ld_a, coop_ld_b;
     unsigned*    coop_flags;
-    unsigned*    coop_done; // zero at launch; every transposing warp adds one when its last block is published
+    // Every transposing warp adds one to *coop_done when its last block is published; the word is never cleared (the
+    // launches that use it are ordered by their stream): coop_done_target is what it reads once all warps of THIS
+    // launch have finished, i.e. the total over all launches so far, modulo 2^32.
+    unsigned*    coop_done;
+    unsigned     coop_done_target;
     // The epilogue stores alpha * (A B) + beta * C (three separately rounded operations, C read only when beta != 0).
     // alpha = 1, beta = 0 everywhere except in the vendor-BLAS convention's entry, which uses other values only without
     // K slices and without further destinations.
@@ -788,7 +792,6 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
         // words of the transposed blocks the copy-issuing thread has to see before it may fetch a stage
         const int  coop_xa = w.coop_src_a ? p.grid_m : 0, coop_xt = coop_xa + (w.coop_src_b ? p.grid_n : 0);
         bool       coop    = w.coop_flags != nullptr && !manual_a && !manual_b;
-        const unsigned coop_warps = gridDim.x * (unsigned)(L::PRODUCERS / 32 - 1);
         int      s     = 0; // ring position
         uint32_t phase = 0; // parity of the current lap
         WsSchedule sch;
@@ -835,7 +838,7 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                         // from then on nothing needs checking any more)
                         const unsigned va = ld_acquire_u32(fa), vb = ld_acquire_u32(fb);
                         bool           got = va == w.epoch && vb == w.epoch;
-                        if(got && (t & 7) == 0 && ld_acquire_u32(w.coop_done) == coop_warps)
+                        if(got && (t & 7) == 0 && ld_acquire_u32(w.coop_done) == w.coop_done_target)
                             coop = false;
                         if(!got)
                         {
