@@ -599,7 +599,7 @@ def ours(args, w):
                        "l2": "operands + result (%.0f MB per rank) exceed the 126 MB L2; no explicit flush"
                              % (4.0 * (M * K + K * Nl + M * Nl) / 1e6)},
             "tflops_avg": flops_total / (avg_ms * 1e-3) / 1e12, "tflops_min_time": flops_total / (min_ms * 1e-3) / 1e12,
-            # (on the hosts of this pool about one launch per second of any kernel takes 2 to 3 ms longer: max shows it)
+            # (on some hosts about one launch per second, of any kernel, takes 2 to 3 ms longer: max shows it)
             "launch_ms": {"min": min_ms, "median": median_ms, "avg": avg_ms, "max": max_ms},
             "identity_bit_exact": check, "allgather_ms": allgather_ms,
             "roofline": roofline, "cpu_baseline": cpu_info, "clocks": clocks, "e2e": e2e,
