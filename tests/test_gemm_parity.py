@@ -521,3 +521,33 @@ def test_release_stream_frees_the_arena(sgemm, orc):
     assert torch.equal(dC.view(torch.int32), first.view(torch.int32))
     sgemm.release_stream(s)
     assert sgemm.device_status() == 0
+
+
+def test_transposition_inside_the_kernel_is_repeatable(sgemm, orc):
+    """The flag-word hand-over between the transposing warps and the thread that issues the TMA copies, exercised many
+    times: 40 calls on a problem with 2 x 16 x 64 blocks must all give the bits of the transposition kernel in front
+    (a block read before it was complete would show as a difference)."""
+    M = N = K = 2048
+    la, lb, lc = 0, 1, 0
+    variant = None
+    for i in range(sgemm.num_variants()):
+        p = sgemm.get_variant(i)
+        if ((p.pipeline, p.block_m, p.block_n, p.block_k, p.block_size) == (1, 128, 128, 32, 256)
+                and all(sgemm.has_kernel(i, a, b, lc, True) for a, b in ((0, 1), (1, 1), (1, 0), (0, 0)))):
+            variant = i
+            break
+    if variant is None:
+        pytest.skip("no 128x128x32 warp-specialised variant built for rcr and its transposed forms")
+    g = torch.Generator(device="cuda").manual_seed(81)
+    dA = torch.rand(M * K, generator=g, device="cuda") * 2 - 1
+    dB = torch.rand(K * N, generator=g, device="cuda") * 2 - 1
+    ref = torch.empty(M * N, device="cuda")
+    sgemm.gemm_trial(lc, la, lb, ref, dA, dB, M, N, K, variant, 1, 3 | 4)
+    out = [torch.full((M * N,), float("nan"), device="cuda") for _ in range(4)]
+    for rep in range(40):
+        sgemm.gemm_trial(lc, la, lb, out[rep % 4], dA, dB, M, N, K, variant, 1, 3)
+        if rep % 4 == 3:
+            for o in out:
+                assert torch.equal(o.view(torch.int32), ref.view(torch.int32)), rep
+                o.fill_(float("nan"))
+    assert sgemm.device_status() == 0
