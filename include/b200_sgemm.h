@@ -65,7 +65,10 @@ typedef struct b200_sgemm_params
  * reads (each block once for all CTAs, by producer warps that would otherwise idle); a transposition kernel in
  * front of the product makes it where that does not apply.  About 0.8 % extra time per operand at 4096^3, instead
  * of 3.5 % for transposing every tile where it is consumed.  b200_sgemm_ex never copies an operand: it runs
- * exactly the kernel it is told. */
+ * exactly the kernel it is told.
+ * Not for stream capture: the flag words behind the balanced schedules and the in-kernel transposition carry a
+ * number that the host advances with every call, which a replayed graph would repeat.  (b200_sgemm_ex without a
+ * workspace runs the plain schedule, uses no flag words and can be captured.) */
 int b200_sgemm(int layout_c, int layout_a, int layout_b, float* C, const float* A, const float* B, size_t M, size_t N,
                size_t K, void* cuda_stream);
 
