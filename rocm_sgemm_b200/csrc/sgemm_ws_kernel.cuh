@@ -19,6 +19,10 @@
 //     hardware's zero fill.  Operands that do not meet TMA's alignment
 //     rules (or K tiles other than 32) take the older route through registers: 128-bit global loads /
 //     guarded cp.async issued by all four producer warps.
+//     When the host has rebound a K-contiguous operand to scratch memory that is to hold it as [K][X] (WsArgs::coop_*),
+//     both operands take the TMA route from the start and the three producer warps it leaves idle fill that scratch:
+//     every block of block_x rows x block_k columns is transposed once, by whichever warp of the grid it falls to, K tile
+//     by K tile, and published through a flag word that the copy-issuing thread acquires before it fetches a stage.
 //   * the CTA is persistent and the producers run ahead into the next piece of work while the consumers store C.
 //     Two schedules (WsArgs::sched):
 //       0  work units (tile, K slice) dealt round-robin: blockIdx.x, +gridDim.x, ...
@@ -32,9 +36,9 @@
 //          (tiles >= CTAs), so that no tile is shared by more than two CTAs.
 //       2  the same equal ranges when there are FEWER tiles than CTAs (small or skinny problems): a tile is then shared
 //          by several CTAs, each of which runs its K range as a chain of its own starting from zero.  All but the last
-//          range of a tile are parked; the CTA that owns the last range waits for them and adds them up in ascending
-//          K order (then its own), so the result is the deterministic ordered sum of chains - the arithmetic of
-//          split-K with tile-dependent cut points, which ws_stream_bounds() reports to the host.
+//          range of a tile are parked; the CTA that owns the last range waits for them and adds them to its own chain
+//          in ascending K order, so the result is the deterministic ordered sum of chains - the arithmetic of
+//          split-K with tile-dependent cut points, which ws_stream_cuts() reports to the host.
 //
 // Packed FMA: the B fragment supplies natural pairs of neighbouring columns (64-bit halves of the
 // 128-bit shared-memory read), the A value is duplicated into both halves.  The FMA order keeps the pair
@@ -766,7 +770,6 @@ __global__ void __launch_bounds__(WsLayout<Cfg>::THREADS, Cfg::MIN_BLOCKS)
                     for(long long u = (long long)blockIdx.x * COOP_WARPS + (ptid / 32 - 1); u < units; u += step)
                     {
                         const int kt = (int)(u / xt), x = (int)(u - (long long)kt * xt);
-
                         if(x < xa)
                             CoopTransposer<BM, BK>::run(w.coop_src_a, w.coop_ld_a, const_cast<float*>(p.A), p.lda, p.M,
                                                         p.K, x * BM, kt * BK, lane_p);
